@@ -1,0 +1,164 @@
+// Internal definitions shared by the host side of libfusilli_b200.so:
+// status/error plumbing, the device/buffer objects behind the opaque C handles,
+// and the kernel plan (the lowered form of a validated Fusilli graph).
+#ifndef FB_COMMON_H
+#define FB_COMMON_H
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/fusilli_b200.h"
+#include "kernels/device_types.h"
+
+#define FB_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace fb {
+
+// Records `msg` as the calling thread's last error and returns `code`.
+fb_status fail(fb_status code, const std::string &msg);
+void clear_error();
+
+#define FB_CUDA_OK(expr)                                                       \
+  do {                                                                         \
+    cudaError_t _e = (expr);                                                   \
+    if (_e != cudaSuccess)                                                     \
+      return fb::fail(FB_RUNTIME_FAILURE, std::string(#expr) + ": " +          \
+                                              cudaGetErrorString(_e));         \
+  } while (0)
+
+#define FB_REQUIRE(cond, code, msg)                                            \
+  do {                                                                         \
+    if (!(cond)) return fb::fail((code), (msg));                               \
+  } while (0)
+
+size_t dtype_size(int32_t dtype); // 0 for unsupported types
+const char *dtype_name(int32_t dtype);
+
+} // namespace fb
+
+struct fb_device {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  bool owns_stream = false;
+  int sm_count = 0;
+  uint32_t *error_word = nullptr; // device word set by kernels whose waits ran out
+};
+
+struct fb_buffer {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+  bool owned = false;
+  int ordinal = 0;
+  cudaStream_t stream = nullptr; // stream the allocation is ordered on
+  std::atomic<int> refs{1};
+};
+
+namespace fb {
+
+// ---- plan -------------------------------------------------------------------
+
+struct TensorInfo {
+  std::string name;
+  int32_t dtype = 0, role = 0, rank = 0, arg_index = -1;
+  int64_t dims[FB_MAX_RANK] = {0};
+  int64_t strides[FB_MAX_RANK] = {0};
+  double scalar = 0.0;
+  int64_t ws_offset = -1; // >= 0: materialised in the workspace at this byte offset
+  int64_t phys_elems() const; // elements of the dense physical buffer
+};
+
+struct NodeInfo {
+  std::string name;
+  fb_node_desc d; // d.name is not valid after load; use `name`
+};
+
+enum StepKind : int32_t {
+  STEP_POINTWISE = 1, // standalone elementwise kernel
+  STEP_REDUCTION = 2,
+  STEP_NORM = 3,      // layernorm / rmsnorm
+  STEP_CONTRACT = 4,  // conv fprop/dgrad/wgrad or matmul (+ fused epilogue)
+  STEP_SDPA = 5,
+};
+
+enum Engine : int32_t {
+  ENGINE_SIMT = 0,    // CUDA-core kernels: any dtype/stride the op allows
+  ENGINE_TCGEN05 = 1, // tcgen05/TMEM/TMA kernels: 16-bit operands, aligned shapes
+};
+
+constexpr int kMaxEpilogueOps = 6;
+
+// One fused pointwise op applied to the running value `v` of a contraction.
+struct EpilogueOpInfo {
+  int32_t mode = 0;      // FB_PW_*
+  int32_t operand = -1;  // tensor id of the other input, -1 for unary
+  int32_t value_is_in1 = 0; // running value is IN_1 (operand is IN_0)
+  int32_t out_tensor = -1;  // tensor whose dtype the result is rounded to
+  float fparams[4] = {1.f, 1.f, 20.f, 1.f};
+};
+
+struct Step {
+  int32_t kind = 0;
+  int32_t engine = ENGINE_SIMT;
+  int32_t node = -1;     // index of the (first) node this step executes
+  int32_t out_tensor = -1; // tensor written by the step (after the epilogue)
+  int32_t num_epilogue = 0;
+  EpilogueOpInfo epilogue[kMaxEpilogueOps];
+  int32_t split_k = 1;      // STEP_CONTRACT wgrad: partial sums in the workspace
+  int64_t scratch_offset = -1; // workspace byte offset of this step's scratch
+  int64_t scratch_bytes = 0;
+};
+
+struct Plan {
+  std::string name;
+  std::vector<TensorInfo> tensors;
+  std::vector<NodeInfo> nodes;
+  std::vector<Step> steps;
+  int32_t num_args = 0;
+  size_t workspace_bytes = 0;
+  std::vector<int32_t> arg_tensor; // arg index -> tensor id
+};
+
+// Lowers tensors+nodes (already filled in `plan`) to steps; FB_NOT_IMPLEMENTED
+// for graphs the kernels cannot run.
+fb_status lower(Plan &plan);
+fb_status serialize(const Plan &plan, std::vector<uint8_t> &out);
+fb_status deserialize(const uint8_t *bytes, size_t n, Plan &plan);
+std::string stats_json(const Plan &plan);
+const char *step_kernel_name(const Plan &plan, const Step &s);
+
+// Launchers (defined next to their kernels). `ptr(t)` resolves a tensor id to its
+// device pointer for this execute call.
+struct ExecContext {
+  const Plan *plan;
+  fb_device *dev;
+  void *const *args;
+  uint8_t *workspace;
+  void *tensor_ptr(int32_t id) const;
+  TensorRef ref(int32_t id) const; // pointer + dtype + dims + strides
+};
+
+fb_status launch_pointwise(const ExecContext &cx, const Step &s);
+fb_status launch_reduction(const ExecContext &cx, const Step &s);
+fb_status launch_norm(const ExecContext &cx, const Step &s);
+fb_status launch_contract_simt(const ExecContext &cx, const Step &s);
+fb_status launch_sdpa_simt(const ExecContext &cx, const Step &s);
+fb_status launch_gemm_tc(const ExecContext &cx, const Step &s);
+fb_status launch_conv_tc(const ExecContext &cx, const Step &s);
+fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s);
+
+// Eligibility checks used by the lowering (pure host logic, no device).
+bool gemm_tc_eligible(const Plan &p, const Step &s);
+bool conv_tc_eligible(const Plan &p, const Step &s);
+bool sdpa_tc_eligible(const Plan &p, const Step &s);
+
+// Fills the device-side epilogue description of a contraction step.
+fb_status build_epilogue(const ExecContext &cx, const Step &s, EpilogueDev &out);
+
+} // namespace fb
+
+#endif // FB_COMMON_H

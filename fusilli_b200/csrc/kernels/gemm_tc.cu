@@ -1,0 +1,510 @@
+// Batched 16-bit GEMM on the 5th-generation tensor cores:
+//   C[b] = epilogue(A[b] * B[b]),  A,B bf16 or f16, fp32 accumulation in TMEM.
+//
+// Persistent, warp-specialised, one CTA per SM:
+//   warp 0      TMA producer: per 64-wide K block one A tile (128 x 64) and one B
+//               tile (64 x 256) land in a 4-stage ring of 128B-swizzled shared memory
+//               (cp.async.bulk.tensor, no multicast, zero fill past the edges).
+//   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16 (cta_group::1),
+//               four per K block, accumulating into one of two 256-column TMEM
+//               buffers; tcgen05.commit releases the stage / publishes the tile.
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (one row per thread),
+//               apply the fused pointwise chain (rounding at each declared dtype),
+//               convert and store 64-byte runs. Overlaps the next tile's main loop
+//               through the second TMEM buffer.
+// Operands may be K-major or MN-major (row-major B is MN-major): the layout goes into
+// the shared-memory and instruction descriptors, no transposition pass.
+// Every mbarrier wait is bounded; on expiry the kernel records an error word and
+// drains instead of spinning.
+#include <algorithm>
+#include <mutex>
+
+#include "../common.h"
+#include "sm100.cuh"
+
+namespace fb {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct TcEpiOp {
+  int32_t mode;
+  int32_t kind; // 0 unary, 1 per-column vector, 2 scalar, 3 full tensor laid out like C
+  int32_t value_is_in1;
+  int32_t round_dtype;
+  int32_t dtype;
+  float scalar;
+  const void *ptr;
+  float prm[4];
+};
+
+struct TcEpilogue {
+  int32_t num_ops;
+  int32_t acc_round_dtype;
+  int32_t out_dtype;
+  TcEpiOp ops[kMaxEpiOps];
+};
+
+struct GemmTcParams {
+  int32_t M, N, K, batches;
+  int32_t a_mn_major, b_mn_major;
+  int32_t a_batch_mul, b_batch_mul;
+  int32_t ab_format;
+  int32_t tiles_m, tiles_n, total_tiles;
+  void *out;
+  int64_t ldc, c_bstride;
+  uint32_t *err;
+  TcEpilogue epi;
+};
+
+__device__ __forceinline__ void store_row32(void *out, int out_dtype, int64_t off, const float *v, int valid) {
+  if (out_dtype == FB_DT_FLOAT) {
+    float *o = static_cast<float *>(out) + off;
+    if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<float4 *>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      for (int j = 0; j < valid; ++j) o[j] = v[j];
+    }
+    return;
+  }
+  uint32_t packed[16];
+  if (out_dtype == FB_DT_BFLOAT16) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      packed[j] = *reinterpret_cast<uint32_t *>(&h);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      packed[j] = *reinterpret_cast<uint32_t *>(&h);
+    }
+  }
+  uint16_t *o = static_cast<uint16_t *>(out) + off;
+  if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      reinterpret_cast<uint4 *>(o)[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+  } else {
+    const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
+    for (int j = 0; j < valid; ++j) o[j] = h[j];
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const int tm = tile % p.tiles_m;
+        const int tn = (tile / p.tiles_m) % p.tiles_n;
+        const int b = tile / (p.tiles_m * p.tiles_n);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn_major) {
+            tma_load_3d(sa, &tmap_a, full_bar(s), k0, m0, b * p.a_batch_mul);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_3d(sa + i * (64 * BK * 2), &tmap_a, full_bar(s), m0 + 64 * i, k0, b * p.a_batch_mul);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(sb, &tmap_b, full_bar(s), k0, n0, b * p.b_batch_mul);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_3d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), n0 + 64 * i, k0, b * p.b_batch_mul);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, BN, p.ab_format, p.a_mn_major, p.b_mn_major);
+      // K-major: rows of 128 B, 8-row groups 1024 B apart; a 16-element K step is 32 B.
+      // MN-major: 64-element MN blocks 8 KB apart (LBO), 8-row K groups 1024 B apart;
+      // a 16-element K step is two K groups = 2048 B.
+      const uint32_t a_lbo = p.a_mn_major ? 64 * BK * 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn_major ? 64 * BK * 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+        const int acc = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s)); // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar(acc)); // accumulator complete
+      }
+    }
+  } else {
+    const int q = warp & 3; // TMEM lane quadrant this warp may access
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+      const int tm = tile % p.tiles_m;
+      const int tn = (tile / p.tiles_m) % p.tiles_n;
+      const int b = tile / (p.tiles_m * p.tiles_n);
+      const int acc = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      if (!mbar_wait(tfull_bar(acc), aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int m = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      const int64_t row_off = (int64_t)b * p.c_bstride + (int64_t)m * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        if (c == BN / 32 - 1) {
+          // all of this warp's reads of the accumulator are done: hand it back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+        const int nc = n0 + c * 32;
+        if (m < p.M && nc < p.N) {
+          const int valid = min(32, p.N - nc);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = round_to(__uint_as_float(raw[j]), p.epi.acc_round_dtype);
+#pragma unroll 1
+          for (int o = 0; o < p.epi.num_ops; ++o) {
+            const TcEpiOp &op = p.epi.ops[o];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float other = 0.f;
+              if (op.kind == 1) other = (j < valid) ? load_f(op.ptr, op.dtype, nc + j) : 0.f;
+              else if (op.kind == 2) other = op.scalar;
+              else if (op.kind == 3) other = (j < valid) ? load_f(op.ptr, op.dtype, row_off + nc + j) : 0.f;
+              const float a = op.value_is_in1 ? other : v[j];
+              const float bb = op.value_is_in1 ? v[j] : other;
+              v[j] = round_to(pw_apply_f(op.mode, a, bb, 0.f, op.prm), op.round_dtype);
+            }
+          }
+          store_row32(p.out, p.epi.out_dtype, row_off + nc, v, valid);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+} // namespace
+
+// ---- host ------------------------------------------------------------------------
+
+namespace sm100 {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                       const uint64_t *strides_bytes, const uint32_t *box, const char **why) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    *why = "cuTensorMapEncodeTiled entry point not available";
+    return false;
+  }
+  cuuint64_t gdims[5], gstr[4];
+  cuuint32_t gbox[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, (cuuint32_t)rank, const_cast<void *>(base), gdims, gstr,
+                  gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *why = "cuTensorMapEncodeTiled rejected the tensor map";
+    return false;
+  }
+  return true;
+}
+
+} // namespace sm100
+
+namespace {
+
+struct GemmView {
+  int64_t M, N, K, batches;
+  int a_mn, b_mn;      // operand is MN-major
+  int64_t a_ld, b_ld;  // leading (slow) stride in elements
+  int64_t a_bs, b_bs;  // batch strides (0 = broadcast)
+  int64_t ldc, c_bs;
+};
+
+bool is16(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16; }
+bool isfl(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16 || dt == FB_DT_FLOAT; }
+
+// Collapses the batch dims of `t` into (count, stride); false if they are not a
+// dense run (or a pure broadcast).
+bool batch_collapse(const TensorInfo &t, const TensorInfo &full, int64_t &stride) {
+  int nb = t.rank - 2;
+  bool all_one = true;
+  for (int i = 0; i < nb; ++i)
+    if (t.dims[i] != 1) all_one = false;
+  if (all_one) {
+    stride = 0;
+    return true;
+  }
+  for (int i = 0; i < nb; ++i)
+    if (t.dims[i] != full.dims[i]) return false; // partial broadcast
+  int64_t expect = -1;
+  for (int i = nb - 1; i >= 0; --i) {
+    if (t.dims[i] == 1) continue;
+    if (expect < 0) {
+      stride = t.strides[i];
+      expect = t.strides[i] * t.dims[i];
+    } else {
+      if (t.strides[i] != expect) return false;
+      expect *= t.dims[i];
+    }
+  }
+  return true;
+}
+
+bool gemm_view(const Plan &p, const Step &s, GemmView &g) {
+  const fb_node_desc &d = p.nodes[s.node].d;
+  const TensorInfo &a = p.tensors[d.inputs[0]], &b = p.tensors[d.inputs[1]];
+  const TensorInfo &c0 = p.tensors[d.outputs[0]], &c = p.tensors[s.out_tensor];
+  if (!is16(a.dtype) || a.dtype != b.dtype || !isfl(c.dtype) || !isfl(c0.dtype)) return false;
+  int r = a.rank;
+  g.M = a.dims[r - 2]; g.K = a.dims[r - 1]; g.N = b.dims[r - 1];
+  g.batches = 1;
+  for (int i = 0; i < r - 2; ++i) g.batches *= c.dims[i];
+  // A[m][k]
+  if (a.strides[r - 1] == 1 && (g.M == 1 || a.strides[r - 2] >= g.K)) { g.a_mn = 0; g.a_ld = a.strides[r - 2]; }
+  else if (a.strides[r - 2] == 1 && a.strides[r - 1] >= g.M) { g.a_mn = 1; g.a_ld = a.strides[r - 1]; }
+  else return false;
+  // B[k][n]
+  if (b.strides[r - 2] == 1 && (g.N == 1 || b.strides[r - 1] >= g.K)) { g.b_mn = 0; g.b_ld = b.strides[r - 1]; }
+  else if (b.strides[r - 1] == 1 && b.strides[r - 2] >= g.N) { g.b_mn = 1; g.b_ld = b.strides[r - 2]; }
+  else return false;
+  if (c.strides[r - 1] != 1) return false;
+  g.ldc = c.strides[r - 2];
+  if (!batch_collapse(a, c, g.a_bs) || !batch_collapse(b, c, g.b_bs) || !batch_collapse(c, c, g.c_bs)) return false;
+  if (g.batches == 1) g.a_bs = g.b_bs = g.c_bs = 0;
+  // TMA: 16-byte aligned strides
+  if (g.a_ld % 8 || g.b_ld % 8 || g.a_bs % 8 || g.b_bs % 8) return false;
+  if (g.M >= (1ll << 31) || g.N >= (1ll << 31) || g.K >= (1ll << 31) || g.batches >= 65536) return false;
+  return true;
+}
+
+// Epilogue operands the tensor-core epilogue can address.
+int epi_kind(const Plan &p, const Step &s, const EpilogueOpInfo &op) {
+  if (op.operand < 0) return 0;
+  const TensorInfo &o = p.tensors[op.operand];
+  const TensorInfo &c = p.tensors[s.out_tensor];
+  if (o.role == FB_TENSOR_SCALAR) return 2;
+  bool vec = o.dims[o.rank - 1] == c.dims[c.rank - 1] && o.strides[o.rank - 1] == 1;
+  for (int i = 0; i + 1 < o.rank; ++i)
+    if (o.dims[i] != 1) vec = false;
+  if (vec) return 1;
+  bool full = o.rank == c.rank;
+  for (int i = 0; full && i < c.rank; ++i)
+    if (o.dims[i] != c.dims[i] || (c.dims[i] > 1 && o.strides[i] != c.strides[i])) full = false;
+  if (full) return 3;
+  return -1;
+}
+
+} // namespace
+
+bool gemm_tc_eligible(const Plan &p, const Step &s) {
+  GemmView g;
+  if (!gemm_view(p, s, g)) return false;
+  // tiny problems stay on the CUDA-core kernel: a 128x256 tile would be mostly padding
+  if (g.M < 64 || g.N < 64 || g.K < 32) return false;
+  for (int i = 0; i < s.num_epilogue; ++i) {
+    if (epi_kind(p, s, s.epilogue[i]) < 0) return false;
+    if (!isfl(p.tensors[s.epilogue[i].out_tensor].dtype)) return false;
+    if (s.epilogue[i].operand >= 0 && !isfl(p.tensors[s.epilogue[i].operand].dtype)) return false;
+  }
+  return true;
+}
+
+fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
+  const Plan &plan = *cx.plan;
+  const fb_node_desc &d = plan.nodes[s.node].d;
+  GemmView g;
+  FB_REQUIRE(gemm_view(plan, s, g), FB_INTERNAL_ERROR, "gemm_tcgen05: step is not eligible");
+  const TensorInfo &a = plan.tensors[d.inputs[0]];
+  const void *aptr = cx.tensor_ptr(d.inputs[0]);
+  const void *bptr = cx.tensor_ptr(d.inputs[1]);
+  void *cptr = cx.tensor_ptr(s.out_tensor);
+  FB_REQUIRE(aptr && bptr && cptr, FB_INTERNAL_ERROR, "gemm_tcgen05: tensor has no buffer");
+  FB_REQUIRE(((uintptr_t)aptr % 16 == 0) && ((uintptr_t)bptr % 16 == 0), FB_INVALID_ARGUMENT,
+             "gemm_tcgen05: operand buffers must be 16-byte aligned");
+
+  static thread_local GemmTcParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.batches = (int)g.batches;
+  p.a_mn_major = g.a_mn; p.b_mn_major = g.b_mn;
+  p.a_batch_mul = g.a_bs ? 1 : 0;
+  p.b_batch_mul = g.b_bs ? 1 : 0;
+  p.ab_format = a.dtype == FB_DT_BFLOAT16 ? 1 : 0;
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.batches;
+  FB_REQUIRE(total < (1ll << 31), FB_NOT_IMPLEMENTED, "gemm_tcgen05: too many tiles");
+  p.total_tiles = (int)total;
+  p.out = cptr;
+  p.ldc = g.ldc;
+  p.c_bstride = g.c_bs;
+  p.err = cx.dev->error_word;
+  p.epi.num_ops = s.num_epilogue;
+  p.epi.acc_round_dtype = plan.tensors[d.outputs[0]].dtype;
+  p.epi.out_dtype = plan.tensors[s.out_tensor].dtype;
+  for (int i = 0; i < s.num_epilogue; ++i) {
+    const EpilogueOpInfo &src = s.epilogue[i];
+    TcEpiOp &op = p.epi.ops[i];
+    op.mode = src.mode;
+    op.kind = epi_kind(plan, s, src);
+    op.value_is_in1 = src.value_is_in1;
+    op.round_dtype = plan.tensors[src.out_tensor].dtype;
+    memcpy(op.prm, src.fparams, sizeof(op.prm));
+    if (src.operand >= 0) {
+      const TensorInfo &o = plan.tensors[src.operand];
+      op.dtype = o.dtype;
+      if (op.kind == 2) op.scalar = (float)o.scalar;
+      else {
+        op.ptr = cx.tensor_ptr(src.operand);
+        FB_REQUIRE(op.ptr != nullptr, FB_INTERNAL_ERROR, "gemm_tcgen05: epilogue operand has no buffer");
+      }
+    }
+  }
+
+  CUtensorMap tmA, tmB;
+  const char *why = "";
+  {
+    // innermost-first dims; a broadcast operand gets a batch extent of 1
+    uint64_t ab = g.a_bs ? (uint64_t)g.batches : 1, bb = g.b_bs ? (uint64_t)g.batches : 1;
+    uint64_t a_bstride = g.a_bs ? (uint64_t)g.a_bs * 2 : (uint64_t)g.a_ld * 2 * (g.a_mn ? g.K : g.M);
+    uint64_t b_bstride = g.b_bs ? (uint64_t)g.b_bs * 2 : (uint64_t)g.b_ld * 2 * (g.b_mn ? g.K : g.N);
+    if (!g.a_mn) {
+      uint64_t dims[3] = {(uint64_t)g.K, (uint64_t)g.M, ab}, str[2] = {(uint64_t)g.a_ld * 2, a_bstride};
+      uint32_t box[3] = {BK, BM, 1};
+      FB_REQUIRE(encode_tmap_2byte(&tmA, aptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
+    } else {
+      uint64_t dims[3] = {(uint64_t)g.M, (uint64_t)g.K, ab}, str[2] = {(uint64_t)g.a_ld * 2, a_bstride};
+      uint32_t box[3] = {64, BK, 1};
+      FB_REQUIRE(encode_tmap_2byte(&tmA, aptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
+    }
+    if (!g.b_mn) {
+      uint64_t dims[3] = {(uint64_t)g.K, (uint64_t)g.N, bb}, str[2] = {(uint64_t)g.b_ld * 2, b_bstride};
+      uint32_t box[3] = {BK, BN, 1};
+      FB_REQUIRE(encode_tmap_2byte(&tmB, bptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
+    } else {
+      uint64_t dims[3] = {(uint64_t)g.N, (uint64_t)g.K, bb}, str[2] = {(uint64_t)g.b_ld * 2, b_bstride};
+      uint32_t box[3] = {64, BK, 1};
+      FB_REQUIRE(encode_tmap_2byte(&tmB, bptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
+    }
+  }
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  // per-device attribute; cheap enough to set on every launch of a new device
+  attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  FB_REQUIRE(attr_err == cudaSuccess, FB_RUNTIME_FAILURE,
+             std::string("gemm_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
+  (void)attr_once;
+  int grid = std::min<int>(p.total_tiles, cx.dev->sm_count);
+  gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+  return FB_OK;
+}
+
+} // namespace fb

@@ -1,0 +1,275 @@
+// LayerNorm (inference and training outputs) and RMSNorm over all non-batch dims.
+//
+// X is contiguous or channels-last, so each sample is one dense run of R
+// elements; one CTA owns one sample. HBM-bound: the row kernel reads the row once
+// with 128-bit loads into registers, reduces in fp32 (warp shuffles + shared
+// memory), and writes once -- 2 * R * sizeof(T) bytes of traffic per row, the
+// algorithmic minimum. Statistics are two-pass over the register copy (mean, then
+// centred sum of squares), so there is no cancellation. The generic kernel
+// re-reads the row from L2 instead and handles any row length and layouts where
+// scale/bias/Y are ordered differently from X.
+#include "../common.h"
+
+namespace fb {
+
+struct NormParams {
+  const void *x, *scale, *bias;
+  void *y, *mean, *rstd;
+  int32_t x_dtype, y_dtype, scale_dtype, bias_dtype, mean_dtype, rstd_dtype;
+  int32_t is_rms;
+  int32_t n_inner;   // rank - 1
+  float eps;
+  int64_t batch, row;
+  int64_t x_bstride, y_bstride;
+  int64_t inner_dims[FB_MAX_RANK]; // non-batch dims in X's physical order, slowest first
+  int64_t y_istr[FB_MAX_RANK], s_istr[FB_MAX_RANK], b_istr[FB_MAX_RANK];
+  int32_t same_order; // Y, scale, bias are all laid out like X within a row
+};
+
+__device__ __forceinline__ float block_sum(float v, float *smem) {
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  int warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  __syncthreads(); // smem may still be read from a previous call
+  if ((threadIdx.x & 31) == 0) smem[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nwarp; ++w) t += smem[w];
+  return t;
+}
+
+__global__ void __launch_bounds__(256) norm_generic_kernel(const NormParams p) {
+  __shared__ float smem[8];
+  for (int64_t b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    const int64_t xb = b * p.x_bstride;
+    float mean = 0.f;
+    if (!p.is_rms) {
+      float s = 0.f;
+      for (int64_t i = threadIdx.x; i < p.row; i += blockDim.x) s += load_f(p.x, p.x_dtype, xb + i);
+      mean = block_sum(s, smem) / (float)p.row;
+    }
+    float ss = 0.f;
+    for (int64_t i = threadIdx.x; i < p.row; i += blockDim.x) {
+      float dlt = load_f(p.x, p.x_dtype, xb + i) - mean;
+      ss += dlt * dlt;
+    }
+    float rstd = rsqrtf(block_sum(ss, smem) / (float)p.row + p.eps);
+    for (int64_t i = threadIdx.x; i < p.row; i += blockDim.x) {
+      int64_t yo = i, so = i, bo = i;
+      if (!p.same_order) {
+        int64_t rem = i;
+        yo = so = bo = 0;
+        for (int d = p.n_inner - 1; d >= 0; --d) {
+          int64_t c = rem % p.inner_dims[d];
+          rem /= p.inner_dims[d];
+          yo += c * p.y_istr[d];
+          so += c * p.s_istr[d];
+          bo += c * p.b_istr[d];
+        }
+      }
+      float v = (load_f(p.x, p.x_dtype, xb + i) - mean) * rstd;
+      if (p.scale) v *= load_f(p.scale, p.scale_dtype, so);
+      if (p.bias) v += load_f(p.bias, p.bias_dtype, bo);
+      store_f(p.y, p.y_dtype, b * p.y_bstride + yo, v);
+    }
+    if (threadIdx.x == 0) {
+      if (p.mean) store_f(p.mean, p.mean_dtype, b, mean);
+      if (p.rstd) store_f(p.rstd, p.rstd_dtype, b, rstd);
+    }
+  }
+}
+
+template <typename T> __device__ __forceinline__ float nelem_f(T x);
+template <> __device__ __forceinline__ float nelem_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float nelem_f<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float nelem_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T nelem_from(float x);
+template <> __device__ __forceinline__ float nelem_from<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half nelem_from<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 nelem_from<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// Loads N consecutive parameters (scale or bias) as floats; P = parameter type.
+template <typename P, int N> __device__ __forceinline__ void load_params(const void *base, int64_t off, float *out) {
+  const P *q = static_cast<const P *>(base) + off;
+  constexpr int BYTES = N * sizeof(P);
+  if constexpr (BYTES == 16) {
+    uint4 r = __ldg(reinterpret_cast<const uint4 *>(q));
+    const P *e = reinterpret_cast<const P *>(&r);
+#pragma unroll
+    for (int j = 0; j < N; ++j) out[j] = nelem_f<P>(e[j]);
+  } else if constexpr (BYTES == 32) {
+    uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(q)), r1 = __ldg(reinterpret_cast<const uint4 *>(q) + 1);
+    const P *e0 = reinterpret_cast<const P *>(&r0), *e1 = reinterpret_cast<const P *>(&r1);
+#pragma unroll
+    for (int j = 0; j < N / 2; ++j) {
+      out[j] = nelem_f<P>(e0[j]);
+      out[N / 2 + j] = nelem_f<P>(e1[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) out[j] = nelem_f<P>(q[j]);
+  }
+}
+
+// Row kernel: T = X and Y element type, P = scale/bias element type, V = 16-byte
+// vectors per thread (row == 256 * V * (16 / sizeof(T))).
+template <typename T, typename P, int V>
+__global__ void __launch_bounds__(256) norm_rows_kernel(const NormParams p) {
+  constexpr int N = 16 / sizeof(T);
+  __shared__ float smem[8];
+  const float inv_row = 1.f / (float)p.row;
+  for (int64_t b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    const uint4 *xr = reinterpret_cast<const uint4 *>(static_cast<const T *>(p.x) + b * p.x_bstride);
+    uint4 raw[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) raw[v] = __ldg(xr + threadIdx.x + v * 256);
+    float f[V][N];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const T *e = reinterpret_cast<const T *>(&raw[v]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        f[v][j] = nelem_f<T>(e[j]);
+        s += f[v][j];
+      }
+    }
+    float mean = 0.f;
+    if (!p.is_rms) mean = block_sum(s, smem) * inv_row;
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        float dlt = f[v][j] - mean;
+        ss += dlt * dlt;
+      }
+    float rstd = rsqrtf(block_sum(ss, smem) * inv_row + p.eps);
+    uint4 *yr = reinterpret_cast<uint4 *>(static_cast<T *>(p.y) + b * p.y_bstride);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      int64_t col = ((int64_t)threadIdx.x + v * 256) * N;
+      float g[N], bt[N];
+      if (p.scale) load_params<P, N>(p.scale, col, g);
+      if (p.bias) load_params<P, N>(p.bias, col, bt);
+      uint4 o;
+      T *oe = reinterpret_cast<T *>(&o);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        float val = (f[v][j] - mean) * rstd;
+        if (p.scale) val *= g[j];
+        if (p.bias) val += bt[j];
+        oe[j] = nelem_from<T>(val);
+      }
+      yr[threadIdx.x + v * 256] = o;
+    }
+    if (threadIdx.x == 0) {
+      if (p.mean) store_f(p.mean, p.mean_dtype, b, mean);
+      if (p.rstd) store_f(p.rstd, p.rstd_dtype, b, rstd);
+    }
+  }
+}
+
+template <typename T, typename P>
+static bool launch_rows(const NormParams &p, int blocks, cudaStream_t st) {
+  constexpr int N = 16 / sizeof(T);
+  int64_t per = 256 * N;
+  if (p.row % per != 0) return false;
+  switch (p.row / per) {
+  case 1: norm_rows_kernel<T, P, 1><<<blocks, 256, 0, st>>>(p); return true;
+  case 2: norm_rows_kernel<T, P, 2><<<blocks, 256, 0, st>>>(p); return true;
+  case 4: norm_rows_kernel<T, P, 4><<<blocks, 256, 0, st>>>(p); return true;
+  case 8: norm_rows_kernel<T, P, 8><<<blocks, 256, 0, st>>>(p); return true;
+  default: return false;
+  }
+}
+
+fb_status launch_norm(const ExecContext &cx, const Step &s) {
+  const Plan &plan = *cx.plan;
+  const fb_node_desc &d = plan.nodes[s.node].d;
+  const bool is_ln = d.op == FB_OP_LAYERNORM;
+  const int xi = d.inputs[0], si = d.inputs[1], bi = is_ln ? d.inputs[2] : -1;
+  const int ei = is_ln ? d.inputs[3] : d.inputs[2];
+  const TensorInfo &x = plan.tensors[xi];
+  const TensorInfo &y = plan.tensors[d.outputs[0]];
+  NormParams p;
+  memset(&p, 0, sizeof(p));
+  p.is_rms = !is_ln;
+  p.eps = (float)plan.tensors[ei].scalar;
+  p.x = cx.tensor_ptr(xi);
+  p.y = cx.tensor_ptr(d.outputs[0]);
+  FB_REQUIRE(p.x && p.y, FB_INTERNAL_ERROR, "norm: tensor has no buffer");
+  p.x_dtype = x.dtype;
+  p.y_dtype = y.dtype;
+  if (si >= 0) {
+    p.scale = cx.tensor_ptr(si);
+    p.scale_dtype = plan.tensors[si].dtype;
+  }
+  if (bi >= 0) {
+    p.bias = cx.tensor_ptr(bi);
+    p.bias_dtype = plan.tensors[bi].dtype;
+  }
+  if (is_ln && (d.flags & FB_FLAG_NORM_TRAINING)) {
+    if (d.outputs[1] >= 0) {
+      p.mean = cx.tensor_ptr(d.outputs[1]);
+      p.mean_dtype = plan.tensors[d.outputs[1]].dtype;
+    }
+    if (d.outputs[2] >= 0) {
+      p.rstd = cx.tensor_ptr(d.outputs[2]);
+      p.rstd_dtype = plan.tensors[d.outputs[2]].dtype;
+    }
+  }
+  p.batch = x.dims[0];
+  p.row = 1;
+  for (int i = 1; i < x.rank; ++i) p.row *= x.dims[i];
+  p.x_bstride = p.row;
+  p.y_bstride = p.row;
+  // inner dims in X's physical order (slowest first)
+  int order[FB_MAX_RANK];
+  int n = 0;
+  for (int i = 1; i < x.rank; ++i) order[n++] = i;
+  for (int i = 1; i < n; ++i)
+    for (int j = i; j > 0 && x.strides[order[j - 1]] < x.strides[order[j]]; --j) {
+      int t = order[j - 1];
+      order[j - 1] = order[j];
+      order[j] = t;
+    }
+  p.n_inner = n;
+  p.same_order = 1;
+  for (int i = 0; i < n; ++i) {
+    int dd = order[i];
+    p.inner_dims[i] = x.dims[dd];
+    p.y_istr[i] = y.strides[dd];
+    if (x.dims[dd] > 1 && y.strides[dd] != x.strides[dd]) p.same_order = 0;
+    if (si >= 0) {
+      p.s_istr[i] = plan.tensors[si].strides[dd];
+      if (x.dims[dd] > 1 && p.s_istr[i] != x.strides[dd]) p.same_order = 0;
+    }
+    if (bi >= 0) {
+      p.b_istr[i] = plan.tensors[bi].strides[dd];
+      if (x.dims[dd] > 1 && p.b_istr[i] != x.strides[dd]) p.same_order = 0;
+    }
+  }
+  cudaStream_t st = cx.dev->stream;
+  int blocks = (int)std::min<int64_t>(p.batch, (int64_t)cx.dev->sm_count * 32);
+  bool aligned = ((uintptr_t)p.x % 16 == 0) && ((uintptr_t)p.y % 16 == 0) &&
+                 (!p.scale || (uintptr_t)p.scale % 16 == 0) && (!p.bias || (uintptr_t)p.bias % 16 == 0);
+  bool params_same = (!p.scale || !p.bias || p.scale_dtype == p.bias_dtype);
+  int pdt = p.scale ? p.scale_dtype : (p.bias ? p.bias_dtype : x.dtype);
+  if (p.same_order && aligned && params_same && x.dtype == y.dtype && (pdt == x.dtype || pdt == FB_DT_FLOAT)) {
+    bool done = false;
+    if (x.dtype == FB_DT_BFLOAT16)
+      done = (pdt == FB_DT_FLOAT) ? launch_rows<__nv_bfloat16, float>(p, blocks, st)
+                                  : launch_rows<__nv_bfloat16, __nv_bfloat16>(p, blocks, st);
+    else if (x.dtype == FB_DT_HALF)
+      done = (pdt == FB_DT_FLOAT) ? launch_rows<__half, float>(p, blocks, st)
+                                  : launch_rows<__half, __half>(p, blocks, st);
+    else if (x.dtype == FB_DT_FLOAT)
+      done = launch_rows<float, float>(p, blocks, st);
+    if (done) return FB_OK;
+  }
+  norm_generic_kernel<<<blocks, 256, 0, st>>>(p);
+  return FB_OK;
+}
+
+} // namespace fb

@@ -271,8 +271,12 @@ def run_ours(args):
     b_local = B_TOTAL // world
     pk = peaks()
 
-    stream = torch.cuda.current_stream()
+    # A dedicated (non-default) torch stream is handed to the backend as its external
+    # stream, so the CUDA events below are recorded on the stream the kernels run on.
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     handle = fz.Handle.create(fz.Backend.CUDA, local, stream.cuda_stream)
+    assert handle.stream() == stream.cuda_stream
     graph, ins, out_t = wl.matmul_bias(b_local, M, N, K, name=f"bench_c2_b{b_local}")
     graph.compile(handle)
     wsz = graph.getWorkspaceSize()

@@ -47,6 +47,9 @@ struct fb_device {
   bool owns_stream = false;
   int sm_count = 0;
   uint32_t *error_word = nullptr; // device word set by kernels whose waits ran out
+  // One reference for the handle itself plus one per live buffer: closing the
+  // handle before its buffers must not pull the stream out from under them.
+  std::atomic<int> refs{1};
 };
 
 struct fb_buffer {
@@ -54,7 +57,7 @@ struct fb_buffer {
   size_t bytes = 0;
   bool owned = false;
   int ordinal = 0;
-  cudaStream_t stream = nullptr; // stream the allocation is ordered on
+  fb_device *dev = nullptr; // retained; its stream orders the allocation and the free
   std::atomic<int> refs{1};
 };
 

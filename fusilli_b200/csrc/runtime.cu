@@ -137,14 +137,21 @@ FB_EXPORT fb_status fb_device_open(int32_t ordinal, void *ext_stream, fb_device 
   return FB_OK;
 }
 
-FB_EXPORT fb_status fb_device_close(fb_device *dev) {
-  clear_error();
-  if (!dev) return FB_OK;
+static void device_unref(fb_device *dev) {
+  if (dev->refs.fetch_sub(1) != 1) return;
   cudaSetDevice(dev->ordinal);
   cudaStreamSynchronize(dev->stream);
   if (dev->error_word) cudaFree(dev->error_word);
   if (dev->owns_stream) cudaStreamDestroy(dev->stream);
   delete dev;
+}
+
+FB_EXPORT fb_status fb_device_close(fb_device *dev) {
+  clear_error();
+  if (!dev) return FB_OK;
+  cudaSetDevice(dev->ordinal);
+  cudaStreamSynchronize(dev->stream);
+  device_unref(dev); // destroyed once the last buffer created on it is released
   return FB_OK;
 }
 
@@ -184,7 +191,8 @@ FB_EXPORT fb_status fb_buffer_alloc(fb_device *dev, size_t bytes, fb_buffer **ou
   b->bytes = bytes;
   b->owned = true;
   b->ordinal = dev->ordinal;
-  b->stream = dev->stream;
+  b->dev = dev;
+  dev->refs.fetch_add(1);
   *out = b;
   return FB_OK;
 }
@@ -200,7 +208,8 @@ FB_EXPORT fb_status fb_buffer_wrap(fb_device *dev, void *dptr, size_t bytes, fb_
   b->bytes = bytes;
   b->owned = false;
   b->ordinal = dev->ordinal;
-  b->stream = dev->stream;
+  b->dev = dev;
+  dev->refs.fetch_add(1);
   *out = b;
   return FB_OK;
 }
@@ -219,8 +228,9 @@ FB_EXPORT fb_status fb_buffer_release(fb_buffer *buf) {
     if (buf->owned && buf->ptr) {
       cudaSetDevice(buf->ordinal);
       // Ordered after the work already queued on the stream it was allocated on.
-      cudaFreeAsync(buf->ptr, buf->stream);
+      cudaFreeAsync(buf->ptr, buf->dev->stream);
     }
+    device_unref(buf->dev);
     delete buf;
   }
   return FB_OK;
@@ -234,7 +244,8 @@ FB_EXPORT fb_status fb_buffer_h2d(fb_device *dev, fb_buffer *buf, const void *sr
                  std::to_string(buf->bytes));
   FB_CUDA_OK(cudaSetDevice(dev->ordinal));
   FB_CUDA_OK(cudaMemcpyAsync(buf->ptr, src, bytes, cudaMemcpyHostToDevice, dev->stream));
-  // Pageable sources are staged before the call returns; pinned sources are not.
+  // Pageable sources are staged before the call returns; pinned sources are not, so
+  // wait for those: the caller may reuse `src` as soon as this returns.
   cudaPointerAttributes attr;
   if (cudaPointerGetAttributes(&attr, src) == cudaSuccess && attr.type == cudaMemoryTypeHost) {
     FB_CUDA_OK(cudaStreamSynchronize(dev->stream));

@@ -156,8 +156,9 @@ class Handle:
 class Buffer:
     """fusilli::Buffer (buffer.h:31-81)."""
 
-    def __init__(self, ptr):
+    def __init__(self, ptr, handle=None):
         self._ptr = ptr
+        self._handle = handle  # keeps the device alive as long as the buffer
 
     @staticmethod
     def allocate(handle: Handle, shape: Sequence[int], data: np.ndarray) -> "Buffer":
@@ -181,7 +182,7 @@ class Buffer:
                                "Buffer::allocateRaw failed: cannot allocate zero-size buffer")
         out = _VP()
         _check(lib().fb_buffer_alloc(handle._ptr, sizeInBytes, ctypes.byref(out)))
-        return Buffer(out)
+        return Buffer(out, handle)
 
     @staticmethod
     def importPointer(handle: Handle, devicePtr: int, sizeInBytes: int) -> "Buffer":
@@ -191,7 +192,7 @@ class Buffer:
                                "Buffer::import failed as externalBufferView* is NULL")
         out = _VP()
         _check(lib().fb_buffer_wrap(handle._ptr, _VP(devicePtr), sizeInBytes, ctypes.byref(out)))
-        return Buffer(out)
+        return Buffer(out, handle)
 
     def write(self, handle: Handle, data: np.ndarray) -> None:
         data = np.ascontiguousarray(data)

@@ -21,6 +21,7 @@
 
 #include "../common.h"
 #include "sm100.cuh"
+#include "tc_epilogue.cuh"
 
 namespace fb {
 
@@ -35,24 +36,6 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barrier
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
-struct TcEpiOp {
-  int32_t mode;
-  int32_t kind; // 0 unary, 1 per-column vector, 2 scalar, 3 full tensor laid out like C
-  int32_t value_is_in1;
-  int32_t round_dtype;
-  int32_t dtype;
-  float scalar;
-  const void *ptr;
-  float prm[4];
-};
-
-struct TcEpilogue {
-  int32_t num_ops;
-  int32_t acc_round_dtype;
-  int32_t out_dtype;
-  TcEpiOp ops[kMaxEpiOps];
-};
-
 struct GemmTcParams {
   int32_t M, N, K, batches;
   int32_t a_mn_major, b_mn_major;
@@ -64,43 +47,6 @@ struct GemmTcParams {
   uint32_t *err;
   TcEpilogue epi;
 };
-
-__device__ __forceinline__ void store_row32(void *out, int out_dtype, int64_t off, const float *v, int valid) {
-  if (out_dtype == FB_DT_FLOAT) {
-    float *o = static_cast<float *>(out) + off;
-    if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        reinterpret_cast<float4 *>(o)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-    } else {
-      for (int j = 0; j < valid; ++j) o[j] = v[j];
-    }
-    return;
-  }
-  uint32_t packed[16];
-  if (out_dtype == FB_DT_BFLOAT16) {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-      packed[j] = *reinterpret_cast<uint32_t *>(&h);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-      packed[j] = *reinterpret_cast<uint32_t *>(&h);
-    }
-  }
-  uint16_t *o = static_cast<uint16_t *>(out) + off;
-  if (valid == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      reinterpret_cast<uint4 *>(o)[j] = make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
-  } else {
-    const uint16_t *h = reinterpret_cast<const uint16_t *>(packed);
-    for (int j = 0; j < valid; ++j) o[j] = h[j];
-  }
-}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -238,22 +184,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const int valid = min(32, p.N - nc);
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = round_to(__uint_as_float(raw[j]), p.epi.acc_round_dtype);
-#pragma unroll 1
-          for (int o = 0; o < p.epi.num_ops; ++o) {
-            const TcEpiOp &op = p.epi.ops[o];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float other = 0.f;
-              if (op.kind == 1) other = (j < valid) ? load_f(op.ptr, op.dtype, nc + j) : 0.f;
-              else if (op.kind == 2) other = op.scalar;
-              else if (op.kind == 3) other = (j < valid) ? load_f(op.ptr, op.dtype, row_off + nc + j) : 0.f;
-              const float a = op.value_is_in1 ? other : v[j];
-              const float bb = op.value_is_in1 ? v[j] : other;
-              v[j] = round_to(pw_apply_f(op.mode, a, bb, 0.f, op.prm), op.round_dtype);
-            }
-          }
-          store_row32(p.out, p.epi.out_dtype, row_off + nc, v, valid);
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          epi_run32(p.epi, v, row_off, nc, valid);
+          epi_store32(p.out, p.epi.out_dtype, row_off + nc, v, valid);
         }
       }
     }

@@ -405,3 +405,138 @@ fb_status launch_contract_simt(const ExecContext &cx, const Step &s) {
 }
 
 } // namespace fb
+
+// ---------------------------------------------------------------------------------
+// Allocation-free weight-gradient entry point.
+//
+// fb_plan_execute takes its split-K scratch from a caller-provided workspace, which
+// somebody had to allocate. Some callers cannot allocate at all at the point where
+// they need the result: code running inside a framework's allocator callback or
+// under its allocator lock, a real-time loop with a no-allocation rule, a plugin
+// that is handed raw device pointers and a stream and nothing else. For them this
+// entry point keeps the scratch in a fixed array inside the library image.
+//
+// The array lives in device memory of every GPU that loads the library, for the
+// life of the process. In host code the name `g_wgrad_static_scratch` is only a
+// handle for the symbol, not a device address, so its address is resolved once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+// ---------------------------------------------------------------------------------
+
+#include <mutex>
+
+namespace fb {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20; // 8 MiB per GPU
+__device__ __align__(256) float g_wgrad_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+float *g_static_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on the CURRENT device (resolved on first use).
+fb_status static_scratch_for_current_device(float **out) {
+  int dev = -1;
+  FB_CUDA_OK(cudaGetDevice(&dev));
+  FB_REQUIRE(dev >= 0 && dev < kMaxDevices, FB_RUNTIME_FAILURE, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_wgrad_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(FB_RUNTIME_FAILURE,
+                  std::string("cudaGetSymbolAddress(static wgrad scratch): ") + cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = static_cast<float *>(p);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return FB_OK;
+}
+
+} // namespace
+} // namespace fb
+
+FB_EXPORT size_t fb_conv_wgrad_static_scratch_bytes(void) { return fb::kStaticScratchBytes; }
+
+FB_EXPORT fb_status fb_conv_wgrad_static(void *stream, const void *dy, const void *x, void *dw, int32_t dtype,
+                                         int32_t n, int32_t c, int32_t h, int32_t w, int32_t k, int32_t r,
+                                         int32_t s, int32_t pad_h, int32_t pad_w, int32_t stride_h,
+                                         int32_t stride_w, int32_t dil_h, int32_t dil_w, int32_t groups) {
+  using namespace fb;
+  clear_error();
+  FB_REQUIRE(dy && x && dw, FB_INVALID_ARGUMENT, "fb_conv_wgrad_static: NULL tensor pointer");
+  FB_REQUIRE(dtype == FB_DT_HALF || dtype == FB_DT_BFLOAT16 || dtype == FB_DT_FLOAT, FB_NOT_IMPLEMENTED,
+             "fb_conv_wgrad_static: dtype must be f16, bf16 or f32");
+  FB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && k > 0 && r > 0 && s > 0 && groups > 0 && stride_h > 0 &&
+                 stride_w > 0 && dil_h > 0 && dil_w > 0 && pad_h >= 0 && pad_w >= 0,
+             FB_INVALID_ARGUMENT, "fb_conv_wgrad_static: non-positive extent");
+  FB_REQUIRE(c % groups == 0 && k % groups == 0, FB_INVALID_ARGUMENT,
+             "fb_conv_wgrad_static: channels must be divisible by groups");
+  const int64_t oh = 1 + ((int64_t)h + 2 * pad_h - (int64_t)(r - 1) * dil_h - 1) / stride_h;
+  const int64_t ow = 1 + ((int64_t)w + 2 * pad_w - (int64_t)(s - 1) * dil_w - 1) / stride_w;
+  FB_REQUIRE(oh > 0 && ow > 0, FB_INVALID_ARGUMENT, "fb_conv_wgrad_static: empty output extent");
+  const int64_t cg = c / groups, kg = k / groups;
+  const int64_t dw_elems = (int64_t)k * cg * r * s;
+  const int64_t red = (int64_t)n * oh * ow;
+  FB_REQUIRE(red < (1ll << 31) && dw_elems < (1ll << 31), FB_NOT_IMPLEMENTED,
+             "fb_conv_wgrad_static: problem extent exceeds 2^31");
+  // Same split heuristic as the planned path, then capped by the fixed scratch.
+  const int64_t tiles = ((kg + BM - 1) / BM) * ((cg * r * s + BN - 1) / BN) * groups;
+  int64_t split = (2 * 148 + tiles - 1) / tiles;
+  split = std::min<int64_t>(split, std::max<int64_t>(red / 256, 1));
+  split = std::min<int64_t>(split, 64);
+  const int64_t max_split = (int64_t)(kStaticScratchBytes / sizeof(float)) / dw_elems;
+  FB_REQUIRE(max_split >= 1, FB_INVALID_ARGUMENT,
+             "fb_conv_wgrad_static: weight gradient of " + std::to_string(dw_elems * 4) +
+                 " bytes (fp32) exceeds the static scratch of " + std::to_string(kStaticScratchBytes) +
+                 " bytes; use the planned path with a caller-provided workspace");
+  split = std::max<int64_t>(1, std::min(split, max_split));
+
+  float *scratch = nullptr;
+  fb_status st = static_scratch_for_current_device(&scratch);
+  if (st != FB_OK) return st;
+
+  static thread_local ContractParams p;
+  memset(&p, 0, sizeof(p));
+  p.mode = CM_WGRAD;
+  p.a = dy; p.b = x; p.out = dw;
+  p.a_dtype = p.b_dtype = dtype;
+  p.epi.num_ops = 0;
+  p.epi.acc_round_dtype = dtype;
+  p.epi.out_dtype = dtype;
+  p.epi.out_rank = 4;
+  ConvGeomDev &g = p.g;
+  g.nsp = 2;
+  g.N = n; g.C = c; g.D = 1; g.H = h; g.W = w;
+  g.K = k; g.Cg = (int32_t)cg; g.Kg = (int32_t)kg; g.T = 1; g.R = r; g.S = s;
+  g.OD = 1; g.OH = (int32_t)oh; g.OW = (int32_t)ow;
+  g.pd = 0; g.ph = pad_h; g.pw = pad_w;
+  g.sd = 1; g.sh = stride_h; g.sw = stride_w;
+  g.dd = 1; g.dh = dil_h; g.dw = dil_w;
+  g.chan_fastest = 1;
+  // dense channels-last tensors: element strides for (n, c, d, h, w)
+  g.xs[0] = (int64_t)h * w * c; g.xs[1] = 1; g.xs[2] = 0; g.xs[3] = (int64_t)w * c; g.xs[4] = c;
+  g.ys[0] = oh * ow * k; g.ys[1] = 1; g.ys[2] = 0; g.ys[3] = ow * k; g.ys[4] = k;
+  g.ws[0] = (int64_t)r * s * cg; g.ws[1] = 1; g.ws[2] = 0; g.ws[3] = (int64_t)s * cg; g.ws[4] = cg;
+  p.G = groups;
+  p.M = kg; p.N = cg * r * s; p.K = red;
+  p.a_kfast = 0; p.b_nfast = 1;
+  p.split_k = (int32_t)split;
+  p.k_chunk = ((p.K + p.split_k - 1) / p.split_k + BK - 1) / BK * BK;
+  // Every element of partial[split][G][M][N] is written by the first kernel before the
+  // second reads it, so the array's previous contents never matter.
+  p.partial = split > 1 ? scratch : nullptr;
+  dim3 grid((unsigned)((p.M + BM - 1) / BM), (unsigned)((p.N + BN - 1) / BN), (unsigned)(p.G * p.split_k));
+  FB_REQUIRE(grid.y <= 65535 && grid.z <= 65535, FB_NOT_IMPLEMENTED,
+             "fb_conv_wgrad_static: problem too large for one launch");
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  contract_simt_kernel<<<grid, 256, 0, cs>>>(p);
+  if (p.split_k > 1) {
+    int64_t total = (int64_t)p.G * p.M * p.N;
+    int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    contract_splitk_reduce_kernel<<<blocks, 256, 0, cs>>>(p);
+  }
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess)
+    return fail(FB_RUNTIME_FAILURE, std::string("fb_conv_wgrad_static: launch failed: ") + cudaGetErrorString(le));
+  return FB_OK;
+}

@@ -76,6 +76,8 @@ ABI_SYMBOLS = [
     ("fb_plan_num_launches", _I32, [_VP, ctypes.POINTER(_I32)]),
     ("fb_plan_stats_json", _I32, [_VP, ctypes.c_char_p, _SZ, ctypes.POINTER(_SZ)]),
     ("fb_plan_execute", _I32, [_VP, _VP, ctypes.POINTER(_VP), ctypes.POINTER(_SZ), _I32, _VP, _SZ]),
+    ("fb_conv_wgrad_static_scratch_bytes", _SZ, []),
+    ("fb_conv_wgrad_static", _I32, [_VP, _VP, _VP, _VP] + [_I32] * 15),
 ]
 
 _lib = None

@@ -313,6 +313,39 @@ fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *args,
  * it with a stream synchronise. */
 fb_status fb_device_kernel_error(fb_device *dev, uint32_t *error_word);
 
+/* ---- allocation-free weight gradient -------------------------------------
+ * No counterpart in the reference: its graphs always run with whatever
+ * transient memory the runtime allocates for them.
+ *
+ * DW = conv weight gradient of dense channels-last tensors (dy NHWC
+ * [n,oh,ow,k], x NHWC [n,h,w,c], dw KRSC [k,r,s,c/groups], all of `dtype` =
+ * FB_DT_HALF / FB_DT_BFLOAT16 / FB_DT_FLOAT, fp32 accumulation), for callers
+ * that must not allocate when they need it: code running inside a framework's
+ * allocator hook or under its allocator lock, a latency-critical loop with a
+ * no-allocation rule, a plugin that only ever receives raw device pointers and a
+ * stream. It takes no fb_device (opening one allocates) and calls no
+ * cudaMalloc/cudaFree or allocating library routine; the partial sums of its
+ * split reduction live in a fixed array of fb_conv_wgrad_static_scratch_bytes()
+ * (8 MiB) inside the library image, resident on every GPU that loads the library
+ * until the process exits.
+ *
+ *  - runs on the CURRENT device, on `stream` (a cudaStream_t, may be NULL);
+ *  - the first call on each device resolves the array's device address; make
+ *    that call before starting any stream capture on that device;
+ *  - fails with FB_INVALID_ARGUMENT when k*(c/groups)*r*s fp32 values do not fit
+ *    in the array -- use a plan with a caller-provided workspace for those;
+ *  - all calls on a device share the one array: two calls whose kernels can
+ *    overlap on the GPU (different streams, no ordering between them) race.
+ *    Calls on the same stream are safe back to back; the array's old contents
+ *    are never read. */
+size_t fb_conv_wgrad_static_scratch_bytes(void);
+fb_status fb_conv_wgrad_static(void *stream, const void *dy, const void *x,
+                               void *dw, int32_t dtype, int32_t n, int32_t c,
+                               int32_t h, int32_t w, int32_t k, int32_t r,
+                               int32_t s, int32_t pad_h, int32_t pad_w,
+                               int32_t stride_h, int32_t stride_w,
+                               int32_t dil_h, int32_t dil_w, int32_t groups);
+
 #ifdef __cplusplus
 }
 #endif

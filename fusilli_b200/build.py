@@ -21,6 +21,7 @@ SOURCES = [
     "kernels/contract_simt.cu",
     "kernels/sdpa_simt.cu",
     "kernels/gemm_tc.cu",
+    "kernels/conv_tc.cu",
     "kernels/tc_stubs.cu",
 ]
 

@@ -1,0 +1,395 @@
+// Implicit-GEMM convolution on the tensor cores: fprop and dgrad of 2-D, stride-1,
+// channels-last (NHWC / KRSC) convolutions with 16-bit operands.
+//
+//   fprop  Y[n,p,q,ko]  = sum_{r,s,c}  X[n, p-pad+r*dil, q-pad+s*dil, c] * W[ko,r,s,c]
+//   dgrad  DX[n,h,w,c]  = sum_{r,s,ko} DY[n, h+pad-r*dil, w+pad-s*dil, ko] * W[ko,r,s,c]
+//
+// No im2col buffer exists anywhere. The GEMM M tile is a rectangular patch of output
+// pixels (bw x bh x bn <= 128 rows); for every filter tap and 64-channel block the TMA
+// producer loads the same patch of the input shifted by the tap offset with ONE tiled
+// 4-D cp.async.bulk.tensor (channels innermost, 128-byte swizzle). Coordinates that
+// fall outside the image are zero-filled by the TMA unit, which is exactly the
+// convolution's padding. 1x1 / pad-0 convolutions collapse (n,h,w) into one axis and
+// run at full tile occupancy. Everything else -- 4-stage ring, one MMA-issuing thread,
+// fp32 accumulators double-buffered in TMEM, register epilogue with the fused pointwise
+// chain, bounded mbarrier waits -- is the batched-GEMM kernel's structure.
+// fprop's filter tile is K-major (c contiguous); dgrad's is MN-major (W[ko][c] rows).
+#include <algorithm>
+
+#include "../common.h"
+#include "sm100.cuh"
+#include "tc_epilogue.cuh"
+
+namespace fb {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, BK = 64, STAGES = 4, MAX_BN = 256;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES_MAX = MAX_BN * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES_MAX;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct ConvTcParams {
+  int32_t dgrad;        // 0 fprop, 1 dgrad
+  int32_t ab_format;    // 0 f16, 1 bf16
+  int32_t N, H, W;      // extents of the OUTPUT pixel space that is tiled
+  int32_t Cred, Nout;   // contraction channels, output channels
+  int32_t R, S;
+  int32_t off_h, off_w, step_h, step_w; // input coord = output coord + off + tap * step
+  int32_t bw, bh, bn, rows;             // patch shape, rows = bw*bh*bn
+  int32_t tiles_w, tiles_h, tiles_nb, tiles_nout, total_tiles;
+  int32_t BN;                            // 64, 128 or 256
+  int32_t cblocks;                       // ceil(Cred / 64)
+  uint32_t a_bytes, b_bytes;
+  void *out;
+  int64_t out_sn, out_sh, out_sw;        // element strides of the output (channel stride 1)
+  uint32_t *err;
+  TcEpilogue epi;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const ConvTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int kblocks = p.R * p.S * p.cblocks;
+  const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        // pixel tiles fastest so that concurrently running CTAs share the filter slice in L2
+        const int tp = tile % tiles_pix, tno = tile / tiles_pix;
+        const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
+        const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn, no0 = tno * p.BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), p.a_bytes + p.b_bytes);
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const int cb = kb % p.cblocks, tap = kb / p.cblocks;
+          const int ts = tap % p.S, tr = tap / p.S;
+          const int c0 = cb * BK;
+          tma_load_4d(sa, &tmap_a, full_bar(s), c0, w0 + p.off_w + ts * p.step_w, h0 + p.off_h + tr * p.step_h, n0);
+          if (!p.dgrad) {
+            // filter rows ko, contraction channel c contiguous: one K-major box
+            tma_load_4d(sb, &tmap_b, full_bar(s), c0, ts, tr, no0);
+          } else {
+            // filter rows ko (contraction), output channel c contiguous: MN-major 64-wide blocks
+            for (int i = 0; i < p.BN / 64; ++i)
+              tma_load_4d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), no0 + 64 * i, ts, tr, c0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 0, p.dgrad);
+      const uint32_t b_lbo = p.dgrad ? 64 * BK * 2 : 16, b_kstep = p.dgrad ? 2048 : 32;
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+        const int acc = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * MAX_BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
+            tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+      const int tp = tile % tiles_pix, tno = tile / tiles_pix;
+      const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
+      const int acc = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      if (!mbar_wait(tfull_bar(acc), aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int row = q * 32 + lane;
+      const int dw = row % p.bw, dh = (row / p.bw) % p.bh, dn = row / (p.bw * p.bh);
+      const int w = tw * p.bw + dw, h = th * p.bh + dh, n = tb * p.bn + dn;
+      const bool row_ok = row < p.rows && w < p.W && h < p.H && n < p.N;
+      const int64_t row_off = (int64_t)n * p.out_sn + (int64_t)h * p.out_sh + (int64_t)w * p.out_sw;
+      const int no0 = tno * p.BN;
+      const uint32_t taddr = tmem_base + acc * MAX_BN + ((uint32_t)(q * 32) << 16);
+      const int nchunks = p.BN / 32;
+#pragma unroll 1
+      for (int c = 0; c < nchunks; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        if (c == nchunks - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+        const int nc = no0 + c * 32;
+        if (row_ok && nc < p.Nout) {
+          const int valid = min(32, p.Nout - nc);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          epi_run32(p.epi, v, row_off, nc, valid);
+          epi_store32(p.out, p.epi.out_dtype, row_off + nc, v, valid);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host -----------------------------------------------------------------------------
+
+struct ConvView {
+  int dgrad;
+  int N, H, W;          // tiled (output) pixel space
+  int IH, IW;           // spatial extent of the tensor the A patches are read from
+  int Cred, Nout, R, S, pad_h, pad_w, dil_h, dil_w;
+  int in_id, w_id;      // tensor ids: activation-like input, filter
+  bool pointwise_1x1;
+};
+
+bool is16(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16; }
+bool isfl(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16 || dt == FB_DT_FLOAT; }
+
+bool channels_last_dense(const TensorInfo &t) {
+  if (t.rank != 4) return false;
+  const int64_t C = t.dims[1], H = t.dims[2], W = t.dims[3];
+  return t.strides[1] == 1 && t.strides[3] == C && t.strides[2] == W * C && t.strides[0] == H * W * C;
+}
+
+bool conv_view(const Plan &p, const Step &s, ConvView &v) {
+  const fb_node_desc &d = p.nodes[s.node].d;
+  if (d.op != FB_OP_CONV_FPROP && d.op != FB_OP_CONV_DGRAD) return false;
+  if (d.num_spatial != 2) return false;
+  if (d.stride[0] != 1 || d.stride[1] != 1) return false;
+  const TensorInfo &in = p.tensors[d.inputs[0]], &w = p.tensors[d.inputs[1]];
+  const TensorInfo &o0 = p.tensors[d.outputs[0]], &out = p.tensors[s.out_tensor];
+  if (!is16(in.dtype) || in.dtype != w.dtype || !isfl(out.dtype) || !isfl(o0.dtype)) return false;
+  if (!channels_last_dense(in) || !channels_last_dense(w) || !channels_last_dense(out)) return false;
+  v.dgrad = d.op == FB_OP_CONV_DGRAD;
+  v.in_id = d.inputs[0];
+  v.w_id = d.inputs[1];
+  v.R = (int)w.dims[2]; v.S = (int)w.dims[3];
+  v.pad_h = (int)d.padding[0]; v.pad_w = (int)d.padding[1];
+  v.dil_h = (int)d.dilation[0]; v.dil_w = (int)d.dilation[1];
+  v.N = (int)out.dims[0]; v.H = (int)out.dims[2]; v.W = (int)out.dims[3];
+  v.IH = (int)in.dims[2]; v.IW = (int)in.dims[3];
+  const int64_t K = w.dims[0], Cf = w.dims[1];
+  if (!v.dgrad) {
+    if (in.dims[1] != Cf) return false; // groups == 1 only
+    v.Cred = (int)Cf; v.Nout = (int)K;
+  } else {
+    if (out.dims[1] != Cf) return false;
+    v.Cred = (int)K; v.Nout = (int)Cf;
+  }
+  if (v.Cred % 8 || v.Nout % 8) return false; // TMA: 16-byte strides
+  if (v.Cred < 64 || v.Nout < 32) return false;
+  if ((int64_t)v.N * v.H * v.W < 128) return false;
+  if (out.dims[0] >= (1 << 30) || (int64_t)v.N * v.H * v.W >= (1ll << 31)) return false;
+  v.pointwise_1x1 = v.R == 1 && v.S == 1 && v.pad_h == 0 && v.pad_w == 0 && v.IH == v.H && v.IW == v.W;
+  return true;
+}
+
+int conv_epi_kind(const Plan &p, const Step &s, const EpilogueOpInfo &op) {
+  if (op.operand < 0) return 0;
+  const TensorInfo &o = p.tensors[op.operand];
+  const TensorInfo &c = p.tensors[s.out_tensor];
+  if (o.role == FB_TENSOR_SCALAR) return 2;
+  if (o.rank == 4 && o.dims[0] == 1 && o.dims[2] == 1 && o.dims[3] == 1 && o.dims[1] == c.dims[1] &&
+      o.strides[1] == 1)
+    return 1;
+  bool full = o.rank == c.rank;
+  for (int i = 0; full && i < c.rank; ++i)
+    if (o.dims[i] != c.dims[i] || (c.dims[i] > 1 && o.strides[i] != c.strides[i])) full = false;
+  return full ? 3 : -1;
+}
+
+// Patch shape (bw, bh, bn) with bw*bh*bn <= 128 that wastes the fewest tile rows.
+void choose_patch(int N, int H, int W, int &bw, int &bh, int &bn) {
+  double best = -1.0;
+  bw = std::min(W, 128); bh = 1; bn = 1;
+  for (int w = 1; w <= std::min(W, 128); ++w) {
+    for (int h = 1; h <= std::min(H, 128 / w); ++h) {
+      int n = 1;
+      if (w == W && h == H) n = std::max(1, std::min(N, 128 / (w * h)));
+      const int64_t tiles = (int64_t)((W + w - 1) / w) * ((H + h - 1) / h) * ((N + n - 1) / n);
+      const double eff = (double)N * H * W / ((double)tiles * 128.0);
+      // prefer wider patches on ties: longer contiguous runs per TMA row
+      if (eff > best + 1e-9 || (eff > best - 1e-9 && w > bw)) {
+        best = eff; bw = w; bh = h; bn = n;
+      }
+    }
+  }
+}
+
+} // namespace
+
+bool conv_tc_eligible(const Plan &p, const Step &s) {
+  ConvView v;
+  if (!conv_view(p, s, v)) return false;
+  for (int i = 0; i < s.num_epilogue; ++i) {
+    if (conv_epi_kind(p, s, s.epilogue[i]) < 0) return false;
+    if (!isfl(p.tensors[s.epilogue[i].out_tensor].dtype)) return false;
+    if (s.epilogue[i].operand >= 0 && !isfl(p.tensors[s.epilogue[i].operand].dtype)) return false;
+  }
+  return true;
+}
+
+fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
+  const Plan &plan = *cx.plan;
+  const fb_node_desc &d = plan.nodes[s.node].d;
+  ConvView v;
+  FB_REQUIRE(conv_view(plan, s, v), FB_INTERNAL_ERROR, "conv_tcgen05: step is not eligible");
+  const TensorInfo &in = plan.tensors[v.in_id], &wt = plan.tensors[v.w_id];
+  const TensorInfo &out = plan.tensors[s.out_tensor];
+  const void *inptr = cx.tensor_ptr(v.in_id);
+  const void *wptr = cx.tensor_ptr(v.w_id);
+  void *optr = cx.tensor_ptr(s.out_tensor);
+  FB_REQUIRE(inptr && wptr && optr, FB_INTERNAL_ERROR, "conv_tcgen05: tensor has no buffer");
+  FB_REQUIRE(((uintptr_t)inptr % 16 == 0) && ((uintptr_t)wptr % 16 == 0), FB_INVALID_ARGUMENT,
+             "conv_tcgen05: operand buffers must be 16-byte aligned");
+
+  static thread_local ConvTcParams p;
+  memset(&p, 0, sizeof(p));
+  p.dgrad = v.dgrad;
+  p.ab_format = in.dtype == FB_DT_BFLOAT16 ? 1 : 0;
+  p.Cred = v.Cred; p.Nout = v.Nout; p.R = v.R; p.S = v.S;
+  p.cblocks = (v.Cred + BK - 1) / BK;
+  p.BN = v.Nout > 128 ? 256 : (v.Nout > 64 ? 128 : 64);
+  // tiled pixel space and the activation tensor as TMA sees it: (C, W, H, N)
+  uint64_t a_dims[4], a_str[3];
+  const int64_t inC = in.dims[1];
+  if (v.pointwise_1x1) {
+    // no halo: (n,h,w) collapses into one axis and every tile is full
+    const int64_t pix = (int64_t)v.N * v.H * v.W;
+    p.N = 1; p.H = 1; p.W = (int32_t)pix;
+    p.bw = 128; p.bh = 1; p.bn = 1;
+    a_dims[0] = inC; a_dims[1] = pix; a_dims[2] = 1; a_dims[3] = 1;
+    a_str[0] = inC * 2; a_str[1] = pix * inC * 2; a_str[2] = pix * inC * 2;
+    p.out_sn = 0; p.out_sh = 0; p.out_sw = out.strides[3];
+  } else {
+    p.N = v.N; p.H = v.H; p.W = v.W;
+    choose_patch(v.N, v.H, v.W, p.bw, p.bh, p.bn);
+    a_dims[0] = inC; a_dims[1] = v.IW; a_dims[2] = v.IH; a_dims[3] = in.dims[0];
+    a_str[0] = inC * 2; a_str[1] = (uint64_t)v.IW * inC * 2; a_str[2] = (uint64_t)v.IH * v.IW * inC * 2;
+    p.out_sn = out.strides[0]; p.out_sh = out.strides[2]; p.out_sw = out.strides[3];
+  }
+  p.rows = p.bw * p.bh * p.bn;
+  if (!v.dgrad) { p.off_h = -v.pad_h; p.off_w = -v.pad_w; p.step_h = v.dil_h; p.step_w = v.dil_w; }
+  else          { p.off_h = v.pad_h;  p.off_w = v.pad_w;  p.step_h = -v.dil_h; p.step_w = -v.dil_w; }
+  p.tiles_w = (p.W + p.bw - 1) / p.bw;
+  p.tiles_h = (p.H + p.bh - 1) / p.bh;
+  p.tiles_nb = (p.N + p.bn - 1) / p.bn;
+  p.tiles_nout = (p.Nout + p.BN - 1) / p.BN;
+  const int64_t total = (int64_t)p.tiles_w * p.tiles_h * p.tiles_nb * p.tiles_nout;
+  FB_REQUIRE(total < (1ll << 31), FB_NOT_IMPLEMENTED, "conv_tcgen05: too many tiles");
+  p.total_tiles = (int)total;
+  p.a_bytes = (uint32_t)p.rows * BK * 2;
+  p.b_bytes = (uint32_t)p.BN * BK * 2;
+  p.out = optr;
+  p.err = cx.dev->error_word;
+  p.epi.num_ops = s.num_epilogue;
+  p.epi.acc_round_dtype = plan.tensors[d.outputs[0]].dtype;
+  p.epi.out_dtype = out.dtype;
+  for (int i = 0; i < s.num_epilogue; ++i) {
+    const EpilogueOpInfo &src = s.epilogue[i];
+    TcEpiOp &op = p.epi.ops[i];
+    op.mode = src.mode;
+    op.kind = conv_epi_kind(plan, s, src);
+    op.value_is_in1 = src.value_is_in1;
+    op.round_dtype = plan.tensors[src.out_tensor].dtype;
+    memcpy(op.prm, src.fparams, sizeof(op.prm));
+    if (src.operand >= 0) {
+      const TensorInfo &o = plan.tensors[src.operand];
+      op.dtype = o.dtype;
+      if (op.kind == 2) op.scalar = (float)o.scalar;
+      else {
+        op.ptr = cx.tensor_ptr(src.operand);
+        FB_REQUIRE(op.ptr != nullptr, FB_INTERNAL_ERROR, "conv_tcgen05: epilogue operand has no buffer");
+      }
+    }
+  }
+  CUtensorMap tmA, tmB;
+  const char *why = "";
+  {
+    uint32_t box[4] = {BK, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
+    FB_REQUIRE(encode_tmap_2byte(&tmA, inptr, 4, a_dims, a_str, box, &why), FB_RUNTIME_FAILURE, why);
+    // filter KRSC as (C, S, R, K)
+    const int64_t Cf = wt.dims[1];
+    uint64_t w_dims[4] = {(uint64_t)Cf, (uint64_t)v.S, (uint64_t)v.R, (uint64_t)wt.dims[0]};
+    uint64_t w_str[3] = {(uint64_t)Cf * 2, (uint64_t)v.S * Cf * 2, (uint64_t)v.R * v.S * Cf * 2};
+    uint32_t wbox_f[4] = {BK, 1, 1, (uint32_t)p.BN};
+    uint32_t wbox_d[4] = {64, 1, 1, BK};
+    FB_REQUIRE(encode_tmap_2byte(&tmB, wptr, 4, w_dims, w_str, v.dgrad ? wbox_d : wbox_f, &why),
+               FB_RUNTIME_FAILURE, why);
+  }
+  cudaError_t ae = cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
+             std::string("conv_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
+  int grid = std::min<int>(p.total_tiles, cx.dev->sm_count);
+  conv_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+  return FB_OK;
+}
+
+} // namespace fb

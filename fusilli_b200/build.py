@@ -22,7 +22,7 @@ SOURCES = [
     "kernels/sdpa_simt.cu",
     "kernels/gemm_tc.cu",
     "kernels/conv_tc.cu",
-    "kernels/tc_stubs.cu",
+    "kernels/sdpa_tc.cu",
 ]
 
 NVCC_FLAGS = [

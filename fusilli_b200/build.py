@@ -22,6 +22,7 @@ SOURCES = [
     "kernels/sdpa_simt.cu",
     "kernels/gemm_tc.cu",
     "kernels/conv_tc.cu",
+    "kernels/conv_wgrad_tc.cu",
     "kernels/sdpa_tc.cu",
 ]
 

@@ -153,11 +153,16 @@ fb_status launch_sdpa_simt(const ExecContext &cx, const Step &s);
 fb_status launch_gemm_tc(const ExecContext &cx, const Step &s);
 fb_status launch_conv_tc(const ExecContext &cx, const Step &s);
 fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s);
+fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s);
 
 // Eligibility checks used by the lowering (pure host logic, no device).
 bool gemm_tc_eligible(const Plan &p, const Step &s);
 bool conv_tc_eligible(const Plan &p, const Step &s);
 bool sdpa_tc_eligible(const Plan &p, const Step &s);
+bool conv_wgrad_tc_eligible(const Plan &p, const Step &s);
+int64_t conv_wgrad_tc_scratch_bytes(const Plan &p, const Step &s, int32_t *slices);
+// Kernel launches one execute of this step issues.
+int step_launches(const Plan &p, const Step &s);
 
 // Fills the device-side epilogue description of a contraction step.
 fb_status build_epilogue(const ExecContext &cx, const Step &s, EpilogueDev &out);

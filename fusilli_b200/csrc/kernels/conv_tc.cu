@@ -271,8 +271,8 @@ void choose_patch(int N, int H, int W, int &bw, int &bh, int &bn) {
   bw = std::min(W, 128); bh = 1; bn = 1;
   for (int w = 1; w <= std::min(W, 128); ++w) {
     for (int h = 1; h <= std::min(H, 128 / w); ++h) {
-      int n = 1;
-      if (w == W && h == H) n = std::max(1, std::min(N, 128 / (w * h)));
+      // the box may span several images: a (w x h) window of n consecutive images
+      const int n = std::max(1, std::min(N, 128 / (w * h)));
       const int64_t tiles = (int64_t)((W + w - 1) / w) * ((H + h - 1) / h) * ((N + n - 1) / n);
       const double eff = (double)N * H * W / ((double)tiles * 128.0);
       // prefer wider patches on ties: longer contiguous runs per TMA row

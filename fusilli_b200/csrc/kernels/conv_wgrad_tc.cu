@@ -1,0 +1,339 @@
+// Weight gradient of 2-D, stride-1, channels-last convolutions on the tensor cores:
+//   DW[ko,r,s,c] = sum_{n,p,q} DY[n,p,q,ko] * X[n, p-pad+r*dil, q-pad+s*dil, c]
+//
+// Per filter tap this is a GEMM with M = ko, N = c and the reduction over output pixels.
+// Both operands are read straight from the NHWC tensors as MN-major tiles: a K block is
+// a patch of 64 output pixels (bw x bh x bn), DY's patch [64 pixels][ko] is the A tile
+// and X's patch shifted by the tap offset [64 pixels][c] is the B tile, each fetched by
+// tiled 4-D TMA with zero fill outside the image (= the padding, and the ragged edge of
+// the pixel space). The A patch is loaded once and reused for every tap of the CTA's tap
+// group; each tap accumulates into its own TMEM columns (taps x BN <= 512).
+// The pixel reduction is split across CTAs: a CTA owns (ko tile, c tile, tap group, pixel
+// slice), writes its fp32 partial filter to the workspace, and a second kernel adds the
+// slices in a fixed order and converts -- deterministic, no atomics.
+#include <algorithm>
+
+#include "../common.h"
+#include "sm100.cuh"
+
+namespace fb {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128, KPIX = 64, A_STAGES = 3, B_STAGES = 4, MAX_BN = 256;
+constexpr int A_STAGE_BYTES = BM * KPIX * 2;     // 16 KB: two 64-channel halves of 64 pixels
+constexpr int B_STAGE_BYTES = MAX_BN * KPIX * 2; // 32 KB
+constexpr int HALF = 64 * KPIX * 2;              // one [64 pixels][64 channels] box
+constexpr int SMEM_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct WgradTcParams {
+  int32_t ab_format;
+  int32_t Kout, C, R, S;
+  int32_t N, P, Q;          // DY pixel space
+  int32_t pad_h, pad_w, dil_h, dil_w;
+  int32_t bw, bh, bn, tiles_w, tiles_h, tiles_nb;
+  int32_t patches_total, patches_per_slice, slices;
+  int32_t k_tiles, c_tiles, ngroups, taps_per_group, BN, a_halves;
+  float *partial;           // [slices][Kout][R*S][C] fp32
+  uint32_t *err;
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
+                          const WgradTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sb_base = smem_base + A_STAGES * A_STAGE_BYTES;
+  const uint32_t bar_base = sb_base + B_STAGES * B_STAGE_BYTES;
+  auto a_full = [&](int s) { return bar_base + 8u * s; };
+  auto a_empty = [&](int s) { return bar_base + 8u * (A_STAGES + s); };
+  auto b_full = [&](int s) { return bar_base + 8u * (2 * A_STAGES + s); };
+  auto b_empty = [&](int s) { return bar_base + 8u * (2 * A_STAGES + B_STAGES + s); };
+  const uint32_t acc_full = bar_base + 8u * (2 * A_STAGES + 2 * B_STAGES);
+  const uint32_t tmem_slot = acc_full + 8u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // unit decomposition: ko tile fastest, then c tile, tap group, pixel slice
+  int u = blockIdx.x;
+  const int kt = u % p.k_tiles; u /= p.k_tiles;
+  const int ct = u % p.c_tiles; u /= p.c_tiles;
+  const int grp = u % p.ngroups;
+  const int slice = u / p.ngroups;
+  const int tap0 = grp * p.taps_per_group;
+  const int ntaps = min(p.taps_per_group, p.R * p.S - tap0);
+  const int patch0 = slice * p.patches_per_slice;
+  const int npatch = min(p.patches_per_slice, p.patches_total - patch0);
+  const uint32_t a_bytes = (uint32_t)p.a_halves * HALF, b_bytes = (uint32_t)p.BN * KPIX * 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < A_STAGES; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+    mbar_init(acc_full, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_dy);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t ia = 0, ib = 0;
+      bool ok = true;
+      for (int pi = 0; pi < npatch && ok; ++pi, ++ia) {
+        const int patch = patch0 + pi;
+        const int tw = patch % p.tiles_w, th = (patch / p.tiles_w) % p.tiles_h, tb = patch / (p.tiles_w * p.tiles_h);
+        const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn;
+        const int sa_i = ia % A_STAGES;
+        if (!mbar_wait(a_empty(sa_i), ((ia / A_STAGES) & 1) ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        mbar_expect_tx(a_full(sa_i), a_bytes);
+        const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
+        for (int hh = 0; hh < p.a_halves; ++hh)
+          tma_load_4d(sa + hh * HALF, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
+        for (int t = 0; t < ntaps; ++t, ++ib) {
+          const int tap = tap0 + t, ts = tap % p.S, tr = tap / p.S;
+          const int sb_i = ib % B_STAGES;
+          if (!mbar_wait(b_empty(sb_i), ((ib / B_STAGES) & 1) ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(b_full(sb_i), b_bytes);
+          const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
+          for (int i = 0; i < p.BN / 64; ++i)
+            tma_load_4d(sb + i * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i, w0 - p.pad_w + ts * p.dil_w,
+                        h0 - p.pad_h + tr * p.dil_h, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 1, 1);
+      uint32_t ia = 0, ib = 0;
+      bool ok = true;
+      for (int pi = 0; pi < npatch && ok; ++pi, ++ia) {
+        const int sa_i = ia % A_STAGES;
+        if (!mbar_wait(a_full(sa_i), (ia / A_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
+        for (int t = 0; t < ntaps; ++t, ++ib) {
+          const int sb_i = ib % B_STAGES;
+          if (!mbar_wait(b_full(sb_i), (ib / B_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < KPIX / 16; ++k) {
+            // both tiles MN-major: 64-channel blocks HALF apart (LBO), 8-pixel groups 1024 B apart,
+            // a 16-pixel K step is 2048 B
+            tc_mma_f16(tmem_base + t * p.BN, make_smem_desc(sa + k * 2048, HALF, 1024),
+                       make_smem_desc(sb + k * 2048, HALF, 1024), idesc, (pi > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(b_empty(sb_i));
+        }
+        if (ok) tc_commit(a_empty(sa_i));
+      }
+      if (ok) tc_commit(acc_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int ko = kt * BM + q * 32 + lane;
+    const int taps_all = p.R * p.S;
+    bool have = npatch > 0;
+    if (have) have = mbar_wait(acc_full, 0, p.err, ERR_WAIT_TMEM_FULL);
+    tc_fence_after();
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    for (int t = 0; t < ntaps; ++t) {
+      for (int cc = 0; cc < p.BN / 32; ++cc) {
+        uint32_t raw[32];
+        if (have) {
+          tmem_ld_32x32(tmem_base + lane_addr + t * p.BN + cc * 32, raw);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) raw[j] = 0u;
+        }
+        const int c0 = ct * p.BN + cc * 32;
+        if (ko < p.Kout && c0 < p.C) {
+          float *dst = p.partial + (((int64_t)slice * p.Kout + ko) * taps_all + (tap0 + t)) * p.C + c0;
+          if (c0 + 32 <= p.C && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              reinterpret_cast<float4 *>(dst)[j] =
+                  make_float4(__uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]),
+                              __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c0 + j < p.C) dst[j] = __uint_as_float(raw[j]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// out[i] = sum over slices of partial[s][i], slice order fixed.
+__global__ void __launch_bounds__(256)
+wgrad_slice_reduce_kernel(const float *__restrict__ partial, void *out, int out_dtype, int64_t elems, int slices) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < slices; ++s) acc += partial[(int64_t)s * elems + i];
+    store_f(out, out_dtype, i, acc);
+  }
+}
+
+bool is16(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16; }
+bool isfl(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16 || dt == FB_DT_FLOAT; }
+
+bool cl_dense(const TensorInfo &t) {
+  if (t.rank != 4) return false;
+  const int64_t C = t.dims[1], H = t.dims[2], W = t.dims[3];
+  return t.strides[1] == 1 && t.strides[3] == C && t.strides[2] == W * C && t.strides[0] == H * W * C;
+}
+
+struct WgradView {
+  int N, P, Q, XH, XW, Kout, C, R, S, pad_h, pad_w, dil_h, dil_w;
+};
+
+bool wgrad_view(const Plan &p, const Step &s, WgradView &v) {
+  const fb_node_desc &d = p.nodes[s.node].d;
+  if (d.op != FB_OP_CONV_WGRAD || d.num_spatial != 2) return false;
+  if (d.stride[0] != 1 || d.stride[1] != 1) return false;
+  if (s.num_epilogue != 0) return false;
+  const TensorInfo &dy = p.tensors[d.inputs[0]], &x = p.tensors[d.inputs[1]], &dw = p.tensors[d.outputs[0]];
+  if (!is16(dy.dtype) || x.dtype != dy.dtype || !isfl(dw.dtype)) return false;
+  if (!cl_dense(dy) || !cl_dense(x) || !cl_dense(dw)) return false;
+  if (dw.dims[1] != x.dims[1]) return false; // groups == 1
+  v.N = (int)dy.dims[0]; v.Kout = (int)dy.dims[1]; v.P = (int)dy.dims[2]; v.Q = (int)dy.dims[3];
+  v.C = (int)x.dims[1]; v.XH = (int)x.dims[2]; v.XW = (int)x.dims[3];
+  v.R = (int)dw.dims[2]; v.S = (int)dw.dims[3];
+  v.pad_h = (int)d.padding[0]; v.pad_w = (int)d.padding[1];
+  v.dil_h = (int)d.dilation[0]; v.dil_w = (int)d.dilation[1];
+  if (v.C % 8 || v.Kout % 8 || v.C < 64 || v.Kout < 64) return false;
+  if ((int64_t)v.N * v.P * v.Q < 4096) return false;
+  return true;
+}
+
+struct WgradTiling {
+  int bw, bh, bn, tiles_w, tiles_h, tiles_nb, patches;
+  int k_tiles, c_tiles, BN, ngroups, taps_per_group, slices, per_slice;
+};
+
+void wgrad_tiling(const WgradView &v, WgradTiling &t) {
+  // 64-pixel patches with power-of-two sides (the K block must be exactly 64 rows)
+  double best = -1.0;
+  t.bw = 8; t.bh = 8; t.bn = 1;
+  for (int w = 1; w <= 64; w *= 2)
+    for (int h = 1; w * h <= 64; h *= 2) {
+      const int n = 64 / (w * h);
+      if (n > v.N && n > 1) continue;
+      const int64_t tiles = (int64_t)((v.Q + w - 1) / w) * ((v.P + h - 1) / h) * ((v.N + n - 1) / n);
+      const double eff = (double)v.N * v.P * v.Q / ((double)tiles * 64.0);
+      if (eff > best + 1e-9 || (eff > best - 1e-9 && w > t.bw)) {
+        best = eff; t.bw = w; t.bh = h; t.bn = n;
+      }
+    }
+  t.tiles_w = (v.Q + t.bw - 1) / t.bw;
+  t.tiles_h = (v.P + t.bh - 1) / t.bh;
+  t.tiles_nb = (v.N + t.bn - 1) / t.bn;
+  t.patches = t.tiles_w * t.tiles_h * t.tiles_nb;
+  t.k_tiles = (v.Kout + BM - 1) / BM;
+  t.BN = v.C > 128 ? 256 : (v.C > 64 ? 128 : 64);
+  t.c_tiles = (v.C + t.BN - 1) / t.BN;
+  const int taps = v.R * v.S;
+  t.ngroups = (taps * t.BN + TMEM_COLS - 1) / TMEM_COLS;
+  t.taps_per_group = (taps + t.ngroups - 1) / t.ngroups;
+  t.ngroups = (taps + t.taps_per_group - 1) / t.taps_per_group;
+  const int units = t.k_tiles * t.c_tiles * t.ngroups;
+  int slices = std::max(1, (2 * 148) / units);
+  slices = std::min(slices, std::max(1, t.patches / 8));
+  t.per_slice = (t.patches + slices - 1) / slices;
+  t.slices = (t.patches + t.per_slice - 1) / t.per_slice;
+}
+
+} // namespace
+
+bool conv_wgrad_tc_eligible(const Plan &p, const Step &s) {
+  WgradView v;
+  return wgrad_view(p, s, v);
+}
+
+// Workspace bytes of the fp32 slice partials (device independent: the plan is built without a device).
+int64_t conv_wgrad_tc_scratch_bytes(const Plan &p, const Step &s, int32_t *slices) {
+  WgradView v;
+  if (!wgrad_view(p, s, v)) return 0;
+  WgradTiling t;
+  wgrad_tiling(v, t);
+  *slices = t.slices;
+  return (int64_t)t.slices * v.Kout * v.R * v.S * v.C * 4;
+}
+
+fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
+  const Plan &plan = *cx.plan;
+  const fb_node_desc &d = plan.nodes[s.node].d;
+  WgradView v;
+  FB_REQUIRE(wgrad_view(plan, s, v), FB_INTERNAL_ERROR, "conv_wgrad_tcgen05: step is not eligible");
+  WgradTiling t;
+  wgrad_tiling(v, t);
+  const TensorInfo &dy = plan.tensors[d.inputs[0]], &dw = plan.tensors[d.outputs[0]];
+  const void *dyp = cx.tensor_ptr(d.inputs[0]), *xp = cx.tensor_ptr(d.inputs[1]);
+  void *dwp = cx.tensor_ptr(s.out_tensor);
+  FB_REQUIRE(dyp && xp && dwp, FB_INTERNAL_ERROR, "conv_wgrad_tcgen05: tensor has no buffer");
+  FB_REQUIRE(((uintptr_t)dyp % 16 == 0) && ((uintptr_t)xp % 16 == 0), FB_INVALID_ARGUMENT,
+             "conv_wgrad_tcgen05: operand buffers must be 16-byte aligned");
+  FB_REQUIRE(cx.workspace && s.scratch_offset >= 0, FB_INTERNAL_ERROR, "conv_wgrad_tcgen05: scratch missing");
+  const int64_t elems = (int64_t)v.Kout * v.R * v.S * v.C;
+  FB_REQUIRE(s.scratch_bytes >= (int64_t)t.slices * elems * 4, FB_INTERNAL_ERROR,
+             "conv_wgrad_tcgen05: scratch smaller than the tiling needs");
+  WgradTcParams p;
+  memset(&p, 0, sizeof(p));
+  p.ab_format = dy.dtype == FB_DT_BFLOAT16 ? 1 : 0;
+  p.Kout = v.Kout; p.C = v.C; p.R = v.R; p.S = v.S;
+  p.N = v.N; p.P = v.P; p.Q = v.Q;
+  p.pad_h = v.pad_h; p.pad_w = v.pad_w; p.dil_h = v.dil_h; p.dil_w = v.dil_w;
+  p.bw = t.bw; p.bh = t.bh; p.bn = t.bn;
+  p.tiles_w = t.tiles_w; p.tiles_h = t.tiles_h; p.tiles_nb = t.tiles_nb;
+  p.patches_total = t.patches; p.patches_per_slice = t.per_slice; p.slices = t.slices;
+  p.k_tiles = t.k_tiles; p.c_tiles = t.c_tiles; p.ngroups = t.ngroups; p.taps_per_group = t.taps_per_group;
+  p.BN = t.BN;
+  p.a_halves = (v.Kout - 0 > 64) ? 2 : 1;
+  p.partial = reinterpret_cast<float *>(cx.workspace + s.scratch_offset);
+  p.err = cx.dev->error_word;
+  CUtensorMap tmDy, tmX;
+  const char *why = "";
+  {
+    uint64_t dims[4] = {(uint64_t)v.Kout, (uint64_t)v.Q, (uint64_t)v.P, (uint64_t)v.N};
+    uint64_t str[3] = {(uint64_t)v.Kout * 2, (uint64_t)v.Q * v.Kout * 2, (uint64_t)v.P * v.Q * v.Kout * 2};
+    uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)t.bh, (uint32_t)t.bn};
+    FB_REQUIRE(encode_tmap_2byte(&tmDy, dyp, 4, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)v.C, (uint64_t)v.XW, (uint64_t)v.XH, (uint64_t)v.N};
+    uint64_t str[3] = {(uint64_t)v.C * 2, (uint64_t)v.XW * v.C * 2, (uint64_t)v.XH * v.XW * v.C * 2};
+    uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)t.bh, (uint32_t)t.bn};
+    FB_REQUIRE(encode_tmap_2byte(&tmX, xp, 4, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
+  }
+  cudaError_t ae =
+      cudaFuncSetAttribute(conv_wgrad_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
+             std::string("conv_wgrad_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
+  const int grid = t.k_tiles * t.c_tiles * t.ngroups * t.slices;
+  conv_wgrad_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmDy, tmX, p);
+  const int rblocks = (int)std::min<int64_t>((elems + 255) / 256, (int64_t)cx.dev->sm_count * 8);
+  wgrad_slice_reduce_kernel<<<rblocks, 256, 0, cx.dev->stream>>>(p.partial, dwp, dw.dtype, elems, t.slices);
+  return FB_OK;
+}
+
+} // namespace fb

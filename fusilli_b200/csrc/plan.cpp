@@ -209,11 +209,14 @@ fb_status lower(Plan &p) {
       }
       if (d.op == FB_OP_MATMUL)
         s.engine = gemm_tc_eligible(p, s) ? ENGINE_TCGEN05 : ENGINE_SIMT;
+      else if (d.op == FB_OP_CONV_WGRAD)
+        s.engine = conv_wgrad_tc_eligible(p, s) ? ENGINE_TCGEN05 : ENGINE_SIMT;
       else
         s.engine = conv_tc_eligible(p, s) ? ENGINE_TCGEN05 : ENGINE_SIMT;
-      if (s.engine == ENGINE_TCGEN05 && d.op != FB_OP_CONV_WGRAD) {
+      if (s.engine == ENGINE_TCGEN05) {
         s.split_k = 1;
         s.scratch_bytes = 0;
+        if (d.op == FB_OP_CONV_WGRAD) s.scratch_bytes = conv_wgrad_tc_scratch_bytes(p, s, &s.split_k);
       }
       break;
     }
@@ -420,10 +423,16 @@ const char *step_kernel_name(const Plan &p, const Step &s) {
   return "unknown";
 }
 
+int step_launches(const Plan &p, const Step &s) {
+  const bool wgrad = p.nodes[s.node].d.op == FB_OP_CONV_WGRAD;
+  if (wgrad && s.engine == ENGINE_TCGEN05) return 2; // partial kernel + slice reduction
+  return s.split_k > 1 ? 2 : 1;
+}
+
 std::string stats_json(const Plan &p) {
   std::ostringstream o;
   int launches = 0;
-  for (const Step &s : p.steps) launches += s.split_k > 1 ? 2 : 1;
+  for (const Step &s : p.steps) launches += step_launches(p, s);
   o << "{\"name\": \"" << p.name << "\", \"dispatch-count\": " << launches
     << ", \"transient-memory-size\": " << p.workspace_bytes << ", \"steps\": [";
   for (size_t i = 0; i < p.steps.size(); ++i) {

@@ -394,7 +394,7 @@ FB_EXPORT fb_status fb_plan_num_launches(fb_plan *plan, int32_t *num_launches) {
   clear_error();
   FB_REQUIRE(plan && num_launches, FB_INVALID_ARGUMENT, "fb_plan_num_launches: NULL argument");
   int n = 0;
-  for (const Step &s : plan->plan.steps) n += (s.split_k > 1) ? 2 : 1;
+  for (const Step &s : plan->plan.steps) n += step_launches(plan->plan, s);
   *num_launches = n;
   return FB_OK;
 }
@@ -449,8 +449,11 @@ FB_EXPORT fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *
     case STEP_REDUCTION: st = launch_reduction(cx, s); break;
     case STEP_NORM: st = launch_norm(cx, s); break;
     case STEP_CONTRACT:
-      if (s.engine == ENGINE_TCGEN05)
-        st = (p.nodes[s.node].d.op == FB_OP_MATMUL) ? launch_gemm_tc(cx, s) : launch_conv_tc(cx, s);
+      if (s.engine == ENGINE_TCGEN05) {
+        const int op = p.nodes[s.node].d.op;
+        st = op == FB_OP_MATMUL ? launch_gemm_tc(cx, s)
+                                : (op == FB_OP_CONV_WGRAD ? launch_conv_wgrad_tc(cx, s) : launch_conv_tc(cx, s));
+      }
       else
         st = launch_contract_simt(cx, s);
       break;

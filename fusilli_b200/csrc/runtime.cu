@@ -370,6 +370,13 @@ FB_EXPORT fb_status fb_plan_load(fb_device *dev, const uint8_t *bytes, size_t nu
   return FB_OK;
 }
 
+FB_EXPORT fb_status fb_plan_check(const uint8_t *bytes, size_t num_bytes) {
+  clear_error();
+  FB_REQUIRE(bytes != nullptr && num_bytes > 0, FB_RUNTIME_FAILURE, "fb_plan_check: empty artifact");
+  Plan p;
+  return deserialize(bytes, num_bytes, p);
+}
+
 FB_EXPORT fb_status fb_plan_free(fb_plan *plan) {
   clear_error();
   delete plan;

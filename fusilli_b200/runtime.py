@@ -71,6 +71,7 @@ ABI_SYMBOLS = [
     ("fb_bytes_free", None, [ctypes.POINTER(ctypes.c_uint8)]),
     ("fb_plan_load", _I32, [_VP, ctypes.c_char_p, _SZ, ctypes.POINTER(_VP)]),
     ("fb_plan_free", _I32, [_VP]),
+    ("fb_plan_check", _I32, [ctypes.c_char_p, _SZ]),
     ("fb_plan_workspace_size", _I32, [_VP, ctypes.POINTER(_SZ)]),
     ("fb_plan_num_args", _I32, [_VP, ctypes.POINTER(_I32)]),
     ("fb_plan_num_launches", _I32, [_VP, ctypes.POINTER(_I32)]),

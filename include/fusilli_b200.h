@@ -290,6 +290,9 @@ void fb_bytes_free(uint8_t *bytes);
 fb_status fb_plan_load(fb_device *dev, const uint8_t *bytes, size_t num_bytes,
                        fb_plan **out);
 fb_status fb_plan_free(fb_plan *plan);
+/* Validates artifact bytes (magic, ABI version, architecture, length, checksum,
+ * payload structure) without a device; the checks fb_plan_load applies. */
+fb_status fb_plan_check(const uint8_t *bytes, size_t num_bytes);
 /* Scratch bytes fb_plan_execute needs (0 when every intermediate is fused). */
 fb_status fb_plan_workspace_size(fb_plan *plan, size_t *bytes);
 /* Number of buffers fb_plan_execute expects in `args`. */

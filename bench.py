@@ -392,7 +392,11 @@ def run_ours(args):
                        "batch_per_gpu": b_local, "l2": f"{nsets} rotating input set(s), {set_bytes * nsets >> 20} MiB > L2",
                        "parallelism": f"batch sharded over {world} GPU(s), no data-path collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tf_burst"], "unit": "TFLOP/s",
-                         "frac": achieved / pk["tf_burst"], "traffic": None, "peak_source": pk["source"],
+                         "frac": achieved / pk["tf_burst"],
+                         # dram__bytes_read+write of one ncu capture at 2 x 4096^3 (196.9 MB,
+                         # profiles/gemm_tcgen05_c2.md), scaled by the matrices one launch processes
+                         "traffic": 196.9e6 * b_local / 2, "traffic_algorithmic": 3.0 * b_local * M * N * 2,
+                         "peak_source": pk["source"],
                          "kernel": "gemm_tcgen05_kernel", "kernel_ms": kern_ms,
                          "frac_of_sustained": achieved / pk["tf_sustained"]},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

@@ -111,57 +111,136 @@ template <typename P, int N> __device__ __forceinline__ void load_params(const v
   }
 }
 
-// Row kernel: T = X and Y element type, P = scale/bias element type, V = 16-byte
-// vectors per thread (row == 256 * V * (16 / sizeof(T))).
-template <typename T, typename P, int V>
-__global__ void __launch_bounds__(256) norm_rows_kernel(const NormParams p) {
+// ---- packed fp32x2 arithmetic (sm_100: one instruction per pair) ---------------------------
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<uint64_t *>(&d))
+      : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)),
+        "l"(*reinterpret_cast<uint64_t *>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 f2_mul(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<uint64_t *>(&d))
+      : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)));
+  return d;
+}
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<uint64_t *>(&d))
+      : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)));
+  return d;
+}
+
+// Element pair `i` of a 16-byte vector as two floats.
+template <typename T> __device__ __forceinline__ float2 vec_pair(const uint4 &r, int i);
+template <> __device__ __forceinline__ float2 vec_pair<float>(const uint4 &r, int i) {
+  const float *f = reinterpret_cast<const float *>(&r);
+  return make_float2(f[2 * i], f[2 * i + 1]);
+}
+template <> __device__ __forceinline__ float2 vec_pair<__nv_bfloat16>(const uint4 &r, int i) {
+  const uint32_t w = reinterpret_cast<const uint32_t *>(&r)[i];
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 vec_pair<__half>(const uint4 &r, int i) {
+  return __half22float2(reinterpret_cast<const __half2 *>(&r)[i]);
+}
+template <typename T> __device__ __forceinline__ void vec_set_pair(uint4 &r, int i, float2 v);
+template <> __device__ __forceinline__ void vec_set_pair<float>(uint4 &r, int i, float2 v) {
+  float *f = reinterpret_cast<float *>(&r);
+  f[2 * i] = v.x;
+  f[2 * i + 1] = v.y;
+}
+template <> __device__ __forceinline__ void vec_set_pair<__nv_bfloat16>(uint4 &r, int i, float2 v) {
+  reinterpret_cast<__nv_bfloat162 *>(&r)[i] = __floats2bfloat162_rn(v.x, v.y);
+}
+template <> __device__ __forceinline__ void vec_set_pair<__half>(uint4 &r, int i, float2 v) {
+  reinterpret_cast<__half2 *>(&r)[i] = __floats2half2_rn(v.x, v.y);
+}
+
+// Sums two values across the CTA with one pair of barriers.
+__device__ __forceinline__ float2 block_sum2(float2 v, float2 *smem) {
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) {
+    v.x += __shfl_xor_sync(0xffffffffu, v.x, m);
+    v.y += __shfl_xor_sync(0xffffffffu, v.y, m);
+  }
+  const int warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) smem[warp] = v;
+  __syncthreads();
+  float2 t = make_float2(0.f, 0.f);
+  for (int w = 0; w < nwarp; ++w) {
+    t.x += smem[w].x;
+    t.y += smem[w].y;
+  }
+  return t;
+}
+
+// Row kernel: T = X and Y element type, P = scale/bias element type, THREADS threads per
+// row, V 16-byte vectors per thread (row == THREADS * V * (16 / sizeof(T))). The row stays
+// PACKED in registers (V uint4). Two sweeps over the registers, both in packed fp32x2:
+//   1. shifted moments: d = x - x0 (x0 = first element of the row), s += d, ss += d*d, one
+//      block reduction for both; mean = x0 + s/n, var = (ss - s*s/n)/n. Shifting by a sample
+//      of the row removes the cancellation of the raw E[x^2] - mean^2 form.
+//   2. y = x * (rstd*gamma) + (beta - mean*rstd*gamma).
+// The kernel is instruction-issue sensitive at HBM speed (64 values per thread): the packed
+// ops and the two-sweep form are what keep it on the bandwidth roof.
+template <typename T, typename P, int V, int THREADS>
+__global__ void __launch_bounds__(THREADS) norm_rows_kernel(const NormParams p) {
   constexpr int N = 16 / sizeof(T);
-  __shared__ float smem[8];
+  constexpr int NP = N / 2;
+  __shared__ float2 smem[8];
   const float inv_row = 1.f / (float)p.row;
   for (int64_t b = blockIdx.x; b < p.batch; b += gridDim.x) {
-    const uint4 *xr = reinterpret_cast<const uint4 *>(static_cast<const T *>(p.x) + b * p.x_bstride);
+    const T *xrow = static_cast<const T *>(p.x) + b * p.x_bstride;
+    const uint4 *xr = reinterpret_cast<const uint4 *>(xrow);
     uint4 raw[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) raw[v] = __ldg(xr + threadIdx.x + v * 256);
-    float f[V][N];
-    float s = 0.f;
+    for (int v = 0; v < V; ++v) raw[v] = __ldg(xr + threadIdx.x + v * THREADS);
+    const float x0 = p.is_rms ? 0.f : nelem_f<T>(__ldg(xrow));
+    const float2 shift = make_float2(-x0, -x0);
+    float2 s2 = make_float2(0.f, 0.f), ss2 = make_float2(0.f, 0.f);
 #pragma unroll
     for (int v = 0; v < V; ++v) {
-      const T *e = reinterpret_cast<const T *>(&raw[v]);
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        f[v][j] = nelem_f<T>(e[j]);
-        s += f[v][j];
+      for (int j = 0; j < NP; ++j) {
+        const float2 d = f2_add(vec_pair<T>(raw[v], j), shift);
+        s2 = f2_add(s2, d);
+        ss2 = f2_fma(d, d, ss2);
       }
     }
-    float mean = 0.f;
-    if (!p.is_rms) mean = block_sum(s, smem) * inv_row;
-    float ss = 0.f;
-#pragma unroll
-    for (int v = 0; v < V; ++v)
-#pragma unroll
-      for (int j = 0; j < N; ++j) {
-        float dlt = f[v][j] - mean;
-        ss += dlt * dlt;
-      }
-    float rstd = rsqrtf(block_sum(ss, smem) * inv_row + p.eps);
+    const float2 tot = block_sum2(make_float2(s2.x + s2.y, ss2.x + ss2.y), smem);
+    float mean = 0.f, var;
+    if (p.is_rms) {
+      var = tot.y * inv_row;
+    } else {
+      const float ds = tot.x * inv_row;
+      mean = x0 + ds;
+      var = fmaxf(tot.y * inv_row - ds * ds, 0.f);
+    }
+    const float rstd = rsqrtf(var + p.eps);
+    const float2 rs2 = make_float2(rstd, rstd), nm2 = make_float2(-mean, -mean);
     uint4 *yr = reinterpret_cast<uint4 *>(static_cast<T *>(p.y) + b * p.y_bstride);
 #pragma unroll
     for (int v = 0; v < V; ++v) {
-      int64_t col = ((int64_t)threadIdx.x + v * 256) * N;
+      const int64_t col = ((int64_t)threadIdx.x + v * THREADS) * N;
       float g[N], bt[N];
       if (p.scale) load_params<P, N>(p.scale, col, g);
       if (p.bias) load_params<P, N>(p.bias, col, bt);
       uint4 o;
-      T *oe = reinterpret_cast<T *>(&o);
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        float val = (f[v][j] - mean) * rstd;
-        if (p.scale) val *= g[j];
-        if (p.bias) val += bt[j];
-        oe[j] = nelem_from<T>(val);
+      for (int j = 0; j < NP; ++j) {
+        float2 a = rs2;
+        if (p.scale) a = f2_mul(make_float2(g[2 * j], g[2 * j + 1]), rs2);
+        float2 c = f2_mul(nm2, a);
+        if (p.bias) c = f2_add(c, make_float2(bt[2 * j], bt[2 * j + 1]));
+        vec_set_pair<T>(o, j, f2_fma(vec_pair<T>(raw[v], j), a, c));
       }
-      yr[threadIdx.x + v * 256] = o;
+      yr[threadIdx.x + v * THREADS] = o;
     }
     if (threadIdx.x == 0) {
       if (p.mean) store_f(p.mean, p.mean_dtype, b, mean);
@@ -171,17 +250,28 @@ __global__ void __launch_bounds__(256) norm_rows_kernel(const NormParams p) {
 }
 
 template <typename T, typename P>
-static bool launch_rows(const NormParams &p, int blocks, cudaStream_t st) {
+static bool launch_rows(const NormParams &p, int sm_count, cudaStream_t st) {
   constexpr int N = 16 / sizeof(T);
-  int64_t per = 256 * N;
-  if (p.row % per != 0) return false;
-  switch (p.row / per) {
-  case 1: norm_rows_kernel<T, P, 1><<<blocks, 256, 0, st>>>(p); return true;
-  case 2: norm_rows_kernel<T, P, 2><<<blocks, 256, 0, st>>>(p); return true;
-  case 4: norm_rows_kernel<T, P, 4><<<blocks, 256, 0, st>>>(p); return true;
-  case 8: norm_rows_kernel<T, P, 8><<<blocks, 256, 0, st>>>(p); return true;
-  default: return false;
+  const int blocks = (int)std::min<int64_t>(p.batch, (int64_t)sm_count * 64);
+  if (p.row % (128 * N) == 0 && p.row / (128 * N) <= 8) {
+    switch (p.row / (128 * N)) {
+    case 1: norm_rows_kernel<T, P, 1, 128><<<blocks, 128, 0, st>>>(p); return true;
+    case 2: norm_rows_kernel<T, P, 2, 128><<<blocks, 128, 0, st>>>(p); return true;
+    case 3: norm_rows_kernel<T, P, 3, 128><<<blocks, 128, 0, st>>>(p); return true;
+    case 4: norm_rows_kernel<T, P, 4, 128><<<blocks, 128, 0, st>>>(p); return true;
+    case 6: norm_rows_kernel<T, P, 6, 128><<<blocks, 128, 0, st>>>(p); return true;
+    case 8: norm_rows_kernel<T, P, 8, 128><<<blocks, 128, 0, st>>>(p); return true;
+    default: break;
+    }
   }
+  if (p.row % (256 * N) == 0) {
+    switch (p.row / (256 * N)) {
+    case 8: norm_rows_kernel<T, P, 8, 256><<<blocks, 256, 0, st>>>(p); return true;
+    case 6: norm_rows_kernel<T, P, 6, 256><<<blocks, 256, 0, st>>>(p); return true;
+    default: break;
+    }
+  }
+  return false;
 }
 
 fb_status launch_norm(const ExecContext &cx, const Step &s) {
@@ -259,13 +349,13 @@ fb_status launch_norm(const ExecContext &cx, const Step &s) {
   if (p.same_order && aligned && params_same && x.dtype == y.dtype && (pdt == x.dtype || pdt == FB_DT_FLOAT)) {
     bool done = false;
     if (x.dtype == FB_DT_BFLOAT16)
-      done = (pdt == FB_DT_FLOAT) ? launch_rows<__nv_bfloat16, float>(p, blocks, st)
-                                  : launch_rows<__nv_bfloat16, __nv_bfloat16>(p, blocks, st);
+      done = (pdt == FB_DT_FLOAT) ? launch_rows<__nv_bfloat16, float>(p, cx.dev->sm_count, st)
+                                  : launch_rows<__nv_bfloat16, __nv_bfloat16>(p, cx.dev->sm_count, st);
     else if (x.dtype == FB_DT_HALF)
-      done = (pdt == FB_DT_FLOAT) ? launch_rows<__half, float>(p, blocks, st)
-                                  : launch_rows<__half, __half>(p, blocks, st);
+      done = (pdt == FB_DT_FLOAT) ? launch_rows<__half, float>(p, cx.dev->sm_count, st)
+                                  : launch_rows<__half, __half>(p, cx.dev->sm_count, st);
     else if (x.dtype == FB_DT_FLOAT)
-      done = launch_rows<float, float>(p, blocks, st);
+      done = launch_rows<float, float>(p, cx.dev->sm_count, st);
     if (done) return FB_OK;
   }
   norm_generic_kernel<<<blocks, 256, 0, st>>>(p);

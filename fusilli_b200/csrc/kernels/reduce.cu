@@ -170,35 +170,35 @@ template <> __device__ __forceinline__ float elem_f<float>(float x) { return x; 
 template <> __device__ __forceinline__ float elem_f<__half>(__half x) { return __half2float(x); }
 template <> __device__ __forceinline__ float elem_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
 
+// 128 threads per row; every thread issues all of its 16-byte loads (up to 8) before it
+// touches the data, so a 16 KB row is completely in flight at once and up to 16 rows per SM.
 template <typename T>
-__global__ void __launch_bounds__(256) reduce_rows_kernel(const T *__restrict__ x, void *y, int y_dtype,
+__global__ void __launch_bounds__(128) reduce_rows_kernel(const T *__restrict__ x, void *y, int y_dtype,
                                                           int64_t y_stride, int64_t rows, int64_t cols,
                                                           int mode) {
   constexpr int N = 16 / sizeof(T);
-  __shared__ float smem[8];
+  constexpr int TH = 128, U = 8;
+  __shared__ float smem[4];
   const int64_t nvec = cols / N;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * cols);
     float acc = red_identity<float>(mode);
-    int64_t i = threadIdx.x;
-    // four independent 16-byte loads in flight per thread
-    for (; i + 3 * 256 < nvec; i += 4 * 256) {
-      uint4 r0 = __ldg(xr + i), r1 = __ldg(xr + i + 256), r2 = __ldg(xr + i + 512), r3 = __ldg(xr + i + 768);
-      const T *e0 = reinterpret_cast<const T *>(&r0), *e1 = reinterpret_cast<const T *>(&r1);
-      const T *e2 = reinterpret_cast<const T *>(&r2), *e3 = reinterpret_cast<const T *>(&r3);
+    for (int64_t base = 0; base < nvec; base += (int64_t)TH * U) {
+      uint4 r[U];
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        acc = red_accum(mode, acc, elem_f<T>(e0[j]));
-        acc = red_accum(mode, acc, elem_f<T>(e1[j]));
-        acc = red_accum(mode, acc, elem_f<T>(e2[j]));
-        acc = red_accum(mode, acc, elem_f<T>(e3[j]));
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = base + threadIdx.x + (int64_t)u * TH;
+        r[u] = i < nvec ? __ldg(xr + i) : make_uint4(0u, 0u, 0u, 0u);
       }
-    }
-    for (; i < nvec; i += 256) {
-      uint4 r0 = __ldg(xr + i);
-      const T *e0 = reinterpret_cast<const T *>(&r0);
 #pragma unroll
-      for (int j = 0; j < N; ++j) acc = red_accum(mode, acc, elem_f<T>(e0[j]));
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = base + threadIdx.x + (int64_t)u * TH;
+        if (i < nvec) {
+          const T *e = reinterpret_cast<const T *>(&r[u]);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc = red_accum(mode, acc, elem_f<T>(e[j]));
+        }
+      }
     }
 #pragma unroll
     for (int m = 16; m >= 1; m >>= 1) acc = red_merge(mode, acc, __shfl_xor_sync(0xffffffffu, acc, m));
@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(256) reduce_rows_kernel(const T *__restrict__ 
     __syncthreads();
     if (threadIdx.x == 0) {
       float t = smem[0];
-      for (int w = 1; w < 8; ++w) t = red_merge(mode, t, smem[w]);
+      for (int w = 1; w < TH / 32; ++w) t = red_merge(mode, t, smem[w]);
       store_f(y, y_dtype, row * y_stride, red_finish(mode, t, cols));
     }
     __syncthreads();
@@ -282,13 +282,13 @@ fb_status launch_reduction(const ExecContext &cx, const Step &s) {
     size_t esz = dtype_size(x.dtype);
     if (rows_ok && cols >= 1024 && (cols * esz) % 16 == 0 && ((uintptr_t)p.x % 16 == 0)) {
       int64_t rows = p.n_out;
-      int blocks = (int)std::min<int64_t>(rows, (int64_t)cx.dev->sm_count * 32);
+      int blocks = (int)std::min<int64_t>(rows, (int64_t)cx.dev->sm_count * 64);
       if (x.dtype == FB_DT_FLOAT)
-        reduce_rows_kernel<float><<<blocks, 256, 0, st>>>((const float *)p.x, p.y, y.dtype, ystride, rows, cols, p.mode);
+        reduce_rows_kernel<float><<<blocks, 128, 0, st>>>((const float *)p.x, p.y, y.dtype, ystride, rows, cols, p.mode);
       else if (x.dtype == FB_DT_HALF)
-        reduce_rows_kernel<__half><<<blocks, 256, 0, st>>>((const __half *)p.x, p.y, y.dtype, ystride, rows, cols, p.mode);
+        reduce_rows_kernel<__half><<<blocks, 128, 0, st>>>((const __half *)p.x, p.y, y.dtype, ystride, rows, cols, p.mode);
       else
-        reduce_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16 *)p.x, p.y, y.dtype, ystride, rows, cols, p.mode);
+        reduce_rows_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16 *)p.x, p.y, y.dtype, ystride, rows, cols, p.mode);
       return FB_OK;
     }
   }

@@ -1,0 +1,3 @@
+// Forwarding header: keeps the reference's include path `fusilli/attributes/reduction_attributes.h` working.
+#pragma once
+#include "../attributes.h"

@@ -1,0 +1,407 @@
+// Matmul, SDPA, LayerNorm, RMSNorm, reduction and pointwise nodes (continuation of nodes.h;
+// include that file, not this one).
+#ifndef FUSILLI_NODES_MORE_H
+#define FUSILLI_NODES_MORE_H
+
+namespace fusilli {
+
+class MatmulNode : public INode {
+public:
+  MatmulAttr matmulAttr;
+  explicit MatmulNode(MatmulAttr &&a) : matmulAttr(std::move(a)) {}
+  const std::string &getName() const override { return matmulAttr.getName(); }
+  Type getType() const override { return Type::Matmul; }
+  ErrorObject validateNode(const Context &ctx) override {
+    auto &m = matmulAttr;
+    TensorPtr a = m.getA(), b = m.getB(), c = m.getC();
+    FUSILLI_RETURN_ERROR_IF(!a, ErrorCode::AttributeNotSet, "Matmul input tensor A not set");
+    FUSILLI_RETURN_ERROR_IF(!b, ErrorCode::AttributeNotSet, "Matmul input tensor B not set");
+    FUSILLI_RETURN_ERROR_IF(!c, ErrorCode::AttributeNotSet, "Matmul output tensor C not set");
+    const auto &ad = a->getDim(), &bd = b->getDim();
+    const size_t ra = ad.size(), rb = bd.size();
+    FUSILLI_RETURN_ERROR_IF(ra < 2, ErrorCode::InvalidAttribute, "Matmul input tensor A must have a rank of at least 2");
+    FUSILLI_RETURN_ERROR_IF(rb < 2, ErrorCode::InvalidAttribute, "Matmul input tensor B must have a rank of at least 2");
+    FUSILLI_RETURN_ERROR_IF(ra != rb, ErrorCode::InvalidAttribute,
+                            "Matmul input tensors A and B must have the same rank: A has rank=" +
+                                std::to_string(ra) + ", B has rank=" + std::to_string(rb));
+    FUSILLI_RETURN_ERROR_IF(ad[ra - 1] != bd[rb - 2], ErrorCode::InvalidAttribute,
+                            "Matmul input tensors A and B have incompatible inner dimensions (K): A has K=" +
+                                std::to_string(ad[ra - 1]) + ", B has K=" + std::to_string(bd[rb - 2]));
+    for (size_t i = 0; i + 2 < ra; ++i)
+      FUSILLI_RETURN_ERROR_IF(!(ad[i] % bd[i] == 0 || bd[i] % ad[i] == 0), ErrorCode::InvalidAttribute,
+                              "Matmul input tensors A and B have incompatible batch dimensions for "
+                              "broadcasting at index " + std::to_string(i) + ": A has dim=" +
+                                  std::to_string(ad[i]) + ", B has dim=" + std::to_string(bd[i]));
+    FUSILLI_CHECK_ERROR(batchDimsOutermost(a, "A"));
+    FUSILLI_CHECK_ERROR(batchDimsOutermost(b, "B"));
+    m.fillFromContext(ctx);
+    if (a->getDataType() != b->getDataType()) {
+      FUSILLI_RETURN_ERROR_IF(ra != 3, ErrorCode::InvalidAttribute,
+                              "Mixed precision matmul is only supported when input tensors A and B are of "
+                              "rank 3 (single batch dim): A and B have rank=" + std::to_string(ra));
+      FUSILLI_RETURN_ERROR_IF(ad[0] != bd[0], ErrorCode::InvalidAttribute,
+                              "Mixed precision matmul input tensors A and B must have exactly equal batch "
+                              "dimensions (no broadcast): A has batch dim=" + std::to_string(ad[0]) +
+                                  ", B has batch dim=" + std::to_string(bd[0]));
+    }
+    const auto inferred = getMatmulInferredOutputShape(ad, bd);
+    if (c->getDim().empty()) c->setDim(inferred);
+    if (c->getStride().empty())
+      c->setStride(generateStrideFromDim(c->getDim(), getContiguousStrideOrder(c->getDim().size())));
+    FUSILLI_RETURN_ERROR_IF(c->getDim().size() < 2, ErrorCode::InvalidAttribute,
+                            "Matmul output tensor C must have a rank of at least 2");
+    FUSILLI_RETURN_ERROR_IF(c->getDim() != inferred, ErrorCode::InvalidAttribute,
+                            "Matmul output tensor C dimensions do not match the expected shapes inferred "
+                            "based on the input dimensions");
+    FUSILLI_CHECK_ERROR(batchDimsOutermost(c, "C"));
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_MATMUL);
+    d.inputs[0] = id(matmulAttr.getA());
+    d.inputs[1] = id(matmulAttr.getB());
+    d.outputs[0] = id(matmulAttr.getC());
+  }
+
+private:
+  static ErrorObject batchDimsOutermost(const TensorPtr &t, const std::string &which) {
+    const auto perm = t->getLogicalToPhysicalPermuteOrder();
+    for (size_t i = 0; i + 2 < t->getDim().size(); ++i)
+      FUSILLI_RETURN_ERROR_IF(perm[i] != static_cast<int64_t>(i), ErrorCode::InvalidAttribute,
+                              "Matmul tensor " + which + " has batch dimensions that are not outermost or "
+                              "are transposed");
+    return ok();
+  }
+};
+
+class SdpaNode : public INode {
+public:
+  SdpaAttr sdpaAttr;
+  explicit SdpaNode(SdpaAttr &&a) : sdpaAttr(std::move(a)) {}
+  const std::string &getName() const override { return sdpaAttr.getName(); }
+  Type getType() const override { return Type::Sdpa; }
+  ErrorObject validateNode(const Context &ctx) override {
+    auto &a = sdpaAttr;
+    TensorPtr q = a.getQ(), k = a.getK(), v = a.getV(), o = a.getO(), mask = a.getMASK();
+    FUSILLI_RETURN_ERROR_IF(!q, ErrorCode::AttributeNotSet, "SDPA input tensor Q not set");
+    FUSILLI_RETURN_ERROR_IF(!k, ErrorCode::AttributeNotSet, "SDPA input tensor K not set");
+    FUSILLI_RETURN_ERROR_IF(!v, ErrorCode::AttributeNotSet, "SDPA input tensor V not set");
+    FUSILLI_RETURN_ERROR_IF(!o, ErrorCode::AttributeNotSet, "SDPA output tensor O not set");
+    FUSILLI_RETURN_ERROR_IF(q->getDim().size() != 4, ErrorCode::InvalidAttribute,
+                            "SDPA input tensor Q must be rank 4 [batch, heads_q, seq_q, head_dim]");
+    FUSILLI_RETURN_ERROR_IF(k->getDim().size() != 4, ErrorCode::InvalidAttribute,
+                            "SDPA input tensor K must be rank 4 [batch, heads_kv, seq_kv, head_dim]");
+    FUSILLI_RETURN_ERROR_IF(v->getDim().size() != 4, ErrorCode::InvalidAttribute,
+                            "SDPA input tensor V must be rank 4 [batch, heads_kv, seq_kv, head_dim]");
+    const auto &qd = q->getDim(), &kd = k->getDim(), &vd = v->getDim();
+    FUSILLI_RETURN_ERROR_IF(qd[0] != kd[0] || qd[0] != vd[0], ErrorCode::InvalidAttribute,
+                            "SDPA input tensors Q, K, V must have matching batch dimension");
+    FUSILLI_RETURN_ERROR_IF(qd[3] != kd[3], ErrorCode::InvalidAttribute,
+                            "SDPA input tensors Q and K must have matching head_dim");
+    FUSILLI_RETURN_ERROR_IF(kd[2] != vd[2], ErrorCode::InvalidAttribute,
+                            "SDPA input tensors K and V must have matching sequence length");
+    const int64_t hq = qd[1], hk = kd[1], hv = vd[1];
+    auto heads = [](int64_t a_, int64_t b_, const char *rel, const char *what) {
+      return std::string("SDPA ") + what + " Q heads (" + std::to_string(a_) + ") " + rel + " heads (" +
+             std::to_string(b_) + ")";
+    };
+    if (a.getEnableGqa()) {
+      FUSILLI_RETURN_ERROR_IF(hq % hk != 0, ErrorCode::InvalidAttribute,
+                              heads(hq, hk, "to be a multiple of K", "with GQA requires"));
+      FUSILLI_RETURN_ERROR_IF(hq % hv != 0, ErrorCode::InvalidAttribute,
+                              heads(hq, hv, "to be a multiple of V", "with GQA requires"));
+    } else {
+      FUSILLI_RETURN_ERROR_IF(hq != hk, ErrorCode::InvalidAttribute,
+                              heads(hq, hk, "to equal K", "without GQA requires"));
+      FUSILLI_RETURN_ERROR_IF(hq != hv, ErrorCode::InvalidAttribute,
+                              heads(hq, hv, "to equal V", "without GQA requires"));
+    }
+    FUSILLI_RETURN_ERROR_IF(mask && a.getIsCausal(), ErrorCode::InvalidAttribute,
+                            "SDPA attention mask and is_causal are mutually exclusive");
+    if (mask) {
+      const auto &md = mask->getDim();
+      FUSILLI_RETURN_ERROR_IF(md.size() != 4, ErrorCode::InvalidAttribute, "SDPA attention mask must be rank 4");
+      const int64_t full[4] = {qd[0], hq, qd[2], kd[2]};
+      const char *what[4] = {"batch dim", "heads dim", "seq_q dim", "seq_kv dim"};
+      for (int i = 0; i < 4; ++i)
+        FUSILLI_RETURN_ERROR_IF(md[i] != 1 && md[i] != full[i], ErrorCode::InvalidAttribute,
+                                std::string("SDPA attention mask ") + what[i] + " (" + std::to_string(md[i]) +
+                                    ") must be 1 or match (" + std::to_string(full[i]) + ")");
+    }
+    FUSILLI_RETURN_ERROR_IF(a.getDropout() < 0.f || a.getDropout() >= 1.f, ErrorCode::InvalidAttribute,
+                            "SDPA dropout probability must be in [0, 1)");
+    a.fillFromContext(ctx);
+    const std::vector<int64_t> od = {qd[0], qd[1], qd[2], vd[3]};
+    if (o->getDim().empty()) o->setDim(od);
+    if (o->getStride().empty()) o->setStride(generateStrideFromDim(od, getContiguousStrideOrder(4)));
+    FUSILLI_RETURN_ERROR_IF(o->getDim() != od, ErrorCode::InvalidAttribute,
+                            "SDPA output tensor O dimensions do not match expected shape "
+                            "[batch, headsQ, seqQ, headDim]");
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_SDPA);
+    d.inputs[0] = id(sdpaAttr.getQ());
+    d.inputs[1] = id(sdpaAttr.getK());
+    d.inputs[2] = id(sdpaAttr.getV());
+    d.inputs[3] = id(sdpaAttr.getMASK());
+    d.outputs[0] = id(sdpaAttr.getO());
+    if (sdpaAttr.getIsCausal()) d.flags |= FB_FLAG_SDPA_CAUSAL;
+    if (sdpaAttr.getEnableGqa()) d.flags |= FB_FLAG_SDPA_GQA;
+    if (sdpaAttr.getScale()) {
+      d.flags |= FB_FLAG_SDPA_HAS_SCALE;
+      d.fparams[0] = *sdpaAttr.getScale();
+    }
+    d.fparams[1] = sdpaAttr.getDropout();
+  }
+};
+
+namespace detail {
+// scale / bias of a norm: X's shape with the batch dim set to 1, X's memory order
+// (reference norm_utils.h:53-99).
+inline void inferScaleBias(const TensorPtr &t, const TensorPtr &x) {
+  if (t->getDim().empty()) {
+    auto d = x->getDim();
+    d[0] = 1;
+    t->setDim(d);
+  }
+  if (t->getStride().empty())
+    t->setStride(generateStrideFromDim(t->getDim(),
+                                       generateStrideOrderPreservingFormat(x->getStride(), t->getDim().size())));
+}
+inline ErrorObject checkScaleBias(const std::string &who, const char *which, const TensorPtr &t, const TensorPtr &x) {
+  if (!t) return ok();
+  if (!t->getDim().empty()) {
+    auto d = x->getDim();
+    d[0] = 1;
+    FUSILLI_RETURN_ERROR_IF(t->getDim() != d, ErrorCode::InvalidAttribute,
+                            who + " input tensor " + which + " must have shape as tensor X with single batch");
+  }
+  if (!t->getStride().empty())
+    FUSILLI_RETURN_ERROR_IF(!layoutOk(t), ErrorCode::NotImplemented, notChannelsLastMsg(t));
+  return ok();
+}
+} // namespace detail
+
+class LayerNormNode : public INode {
+public:
+  LayernormAttr layernormAttr;
+  explicit LayerNormNode(LayernormAttr &&a) : layernormAttr(std::move(a)) {}
+  const std::string &getName() const override { return layernormAttr.getName(); }
+  Type getType() const override { return Type::LayerNorm; }
+  ErrorObject validateNode(const Context &ctx) override {
+    auto &a = layernormAttr;
+    const bool training = a.getForwardPhase() == NormFwdPhase::TRAINING;
+    FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::NOT_SET, ErrorCode::AttributeNotSet,
+                            "LayerNorm forward phase not set");
+    TensorPtr x = a.getX(), s = a.getSCALE(), b = a.getBIAS(), y = a.getY(), m = a.getMEAN(),
+              v = a.getINV_VARIANCE(), e = a.getEpsilon();
+    FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "LayerNorm input tensor X not set");
+    FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "LayerNorm output tensor Y not set");
+    FUSILLI_RETURN_ERROR_IF(x->getDim().size() < 2, ErrorCode::InvalidAttribute,
+                            "LayerNorm input tensor X must have a rank of at least 2");
+    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(x), ErrorCode::NotImplemented, detail::notChannelsLastMsg(x));
+    FUSILLI_CHECK_ERROR(detail::checkScaleBias("LayerNorm", "SCALE", s, x));
+    FUSILLI_CHECK_ERROR(detail::checkScaleBias("LayerNorm", "BIAS", b, x));
+    if (training) {
+      FUSILLI_RETURN_ERROR_IF(!m, ErrorCode::AttributeNotSet, "LayerNorm output tensor MEAN not set");
+      FUSILLI_RETURN_ERROR_IF(!v, ErrorCode::AttributeNotSet, "LayerNorm output tensor INV_VARIANCE not set");
+    } else {
+      FUSILLI_RETURN_ERROR_IF(m != nullptr, ErrorCode::InvalidAttribute, "LayerNorm output tensor MEAN should not be set");
+      FUSILLI_RETURN_ERROR_IF(v != nullptr, ErrorCode::InvalidAttribute,
+                              "LayerNorm output tensor INV_VARIANCE should not be set");
+    }
+    FUSILLI_RETURN_ERROR_IF(!e, ErrorCode::AttributeNotSet, "LayerNorm epsilon not set");
+    FUSILLI_RETURN_ERROR_IF(!e->isScalar(), ErrorCode::InvalidAttribute, "LayerNorm epsilon must be a scalar constant");
+    a.fillFromContext(ctx);
+    if (s) detail::inferScaleBias(s, x);
+    if (b) detail::inferScaleBias(b, x);
+    if (y->getDim().empty()) y->setDim(x->getDim());
+    if (y->getStride().empty()) y->setStride(x->getStride());
+    FUSILLI_RETURN_ERROR_IF(x->getDim() != y->getDim(), ErrorCode::InvalidAttribute,
+                            "LayerNorm output Y tensor must have the same shape as input X tensor");
+    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(y), ErrorCode::NotImplemented, detail::notChannelsLastMsg(y));
+    if (training) {
+      std::vector<int64_t> sd(x->getDim().size(), 1);
+      sd[0] = x->getDim()[0];
+      const auto ss = generateStrideFromDim(sd, getContiguousStrideOrder(sd.size()));
+      for (const TensorPtr &t : {m, v}) {
+        if (t->getDim().empty()) t->setDim(sd);
+        if (t->getStride().empty()) t->setStride(ss);
+      }
+      FUSILLI_RETURN_ERROR_IF(m->getDim() != sd, ErrorCode::InvalidAttribute,
+                              "Layernorm output MEAN tensor must have shape [B, 1, ..., 1] with rank equal to "
+                              "input X tensor's rank, and batch dimension equal to input X tensor's batch dimension");
+      FUSILLI_RETURN_ERROR_IF(v->getDim() != sd, ErrorCode::InvalidAttribute,
+                              "LayerNorm output INV_VARIANCE tensor must have shape [B, 1, ..., 1] with  rank equal "
+                              "to input X tensor's rank, and batch dimension equal to input X tensor's batch dimension");
+      FUSILLI_RETURN_ERROR_IF(m->getStride() != ss, ErrorCode::InvalidAttribute,
+                              "LayerNorm output MEAN tensor must have unit strides");
+      FUSILLI_RETURN_ERROR_IF(v->getStride() != ss, ErrorCode::InvalidAttribute,
+                              "LayerNorm output INV_VARIANCE tensor must have unit strides");
+    }
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_LAYERNORM);
+    d.inputs[0] = id(layernormAttr.getX());
+    d.inputs[1] = id(layernormAttr.getSCALE());
+    d.inputs[2] = id(layernormAttr.getBIAS());
+    d.inputs[3] = id(layernormAttr.getEpsilon());
+    d.outputs[0] = id(layernormAttr.getY());
+    d.outputs[1] = id(layernormAttr.getMEAN());
+    d.outputs[2] = id(layernormAttr.getINV_VARIANCE());
+    if (layernormAttr.getForwardPhase() == NormFwdPhase::TRAINING) d.flags |= FB_FLAG_NORM_TRAINING;
+  }
+};
+
+class RmsNormNode : public INode {
+public:
+  RmsnormAttr rmsnormAttr;
+  explicit RmsNormNode(RmsnormAttr &&a) : rmsnormAttr(std::move(a)) {}
+  const std::string &getName() const override { return rmsnormAttr.getName(); }
+  Type getType() const override { return Type::RmsNorm; }
+  ErrorObject validateNode(const Context &ctx) override {
+    auto &a = rmsnormAttr;
+    FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::NOT_SET, ErrorCode::AttributeNotSet,
+                            "RmsNorm forward phase not set");
+    TensorPtr x = a.getX(), s = a.getSCALE(), y = a.getY(), e = a.getEpsilon();
+    FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "RmsNorm input tensor X not set");
+    FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "RmsNorm output tensor Y not set");
+    FUSILLI_RETURN_ERROR_IF(x->getDim().size() < 2, ErrorCode::InvalidAttribute,
+                            "RmsNorm input tensor X must have a rank of at least 2");
+    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(x), ErrorCode::NotImplemented, detail::notChannelsLastMsg(x));
+    FUSILLI_CHECK_ERROR(detail::checkScaleBias("RmsNorm", "SCALE", s, x));
+    FUSILLI_RETURN_ERROR_IF(!e, ErrorCode::AttributeNotSet, "RmsNorm epsilon not set");
+    FUSILLI_RETURN_ERROR_IF(!e->isScalar(), ErrorCode::InvalidAttribute, "RmsNorm epsilon must be a scalar constant");
+    FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::TRAINING, ErrorCode::NotImplemented,
+                            "RmsNorm training forward phase is not implemented");
+    a.fillFromContext(ctx);
+    if (s) detail::inferScaleBias(s, x);
+    if (y->getDim().empty()) y->setDim(x->getDim());
+    if (y->getStride().empty()) y->setStride(x->getStride());
+    FUSILLI_RETURN_ERROR_IF(x->getDim() != y->getDim(), ErrorCode::InvalidAttribute,
+                            "RmsNorm output Y tensor must have the same shape as input X tensor");
+    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(y), ErrorCode::NotImplemented, detail::notChannelsLastMsg(y));
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_RMSNORM);
+    d.inputs[0] = id(rmsnormAttr.getX());
+    d.inputs[1] = id(rmsnormAttr.getSCALE());
+    d.inputs[2] = id(rmsnormAttr.getEpsilon());
+    d.outputs[0] = id(rmsnormAttr.getY());
+  }
+};
+
+class ReductionNode : public INode {
+public:
+  ReductionAttr reductionAttr;
+  explicit ReductionNode(ReductionAttr &&a) : reductionAttr(std::move(a)) {}
+  const std::string &getName() const override { return reductionAttr.getName(); }
+  Type getType() const override { return Type::Reduction; }
+  // dims i with Y[i] == 1 and X[i] > 1
+  std::vector<int64_t> getReductionDims() const {
+    std::vector<int64_t> dims;
+    const auto &xd = reductionAttr.getX()->getDim(), &yd = reductionAttr.getY()->getDim();
+    for (size_t i = 0; i < xd.size(); ++i)
+      if (yd[i] == 1 && xd[i] > 1) dims.push_back(static_cast<int64_t>(i));
+    return dims;
+  }
+  ErrorObject validateNode(const Context &ctx) override {
+    auto &a = reductionAttr;
+    FUSILLI_RETURN_ERROR_IF(a.getMode() == ReductionAttr::Mode::NOT_SET, ErrorCode::AttributeNotSet,
+                            "Reduction mode not set");
+    TensorPtr x = a.getX(), y = a.getY();
+    FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "Reduction operation requires X input");
+    FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "Reduction operation requires Y output");
+    FUSILLI_RETURN_ERROR_IF(x->getDim().empty(), ErrorCode::AttributeNotSet, "Reduction input X dimensions not set");
+    a.fillFromContext(ctx);
+    if (y->getDim().empty()) y->setDim(x->getDim());
+    if (y->getStride().empty())
+      y->setStride(generateStrideFromDim(y->getDim(), getContiguousStrideOrder(y->getDim().size())));
+    FUSILLI_RETURN_ERROR_IF(x->getDim().size() != y->getDim().size(), ErrorCode::InvalidAttribute,
+                            "Reduction input and output must have the same rank");
+    FUSILLI_RETURN_ERROR_IF(a.getMode() == ReductionAttr::Mode::AVG &&
+                                (isIntegralOrBoolType(x->getDataType()) || isIntegralOrBoolType(y->getDataType())),
+                            ErrorCode::InvalidAttribute,
+                            "Reduction AVG is not supported for integral or boolean tensors");
+    for (size_t i = 0; i < x->getDim().size(); ++i)
+      FUSILLI_RETURN_ERROR_IF(y->getDim()[i] != 1 && y->getDim()[i] != x->getDim()[i], ErrorCode::InvalidAttribute,
+                              "Reduction output dimension " + std::to_string(i) +
+                                  " must be 1 or match input dimension");
+    FUSILLI_RETURN_ERROR_IF(getReductionDims().empty(), ErrorCode::InvalidAttribute,
+                            "Reduction requires at least one dimension to reduce (Y[i] == 1 where X[i] > 1)");
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_REDUCTION);
+    d.mode = static_cast<int32_t>(reductionAttr.getMode());
+    d.inputs[0] = id(reductionAttr.getX());
+    d.outputs[0] = id(reductionAttr.getY());
+  }
+};
+
+class PointwiseNode : public INode {
+public:
+  PointwiseAttr pointwiseAttr;
+  explicit PointwiseNode(PointwiseAttr &&a) : pointwiseAttr(std::move(a)) {}
+  const std::string &getName() const override { return pointwiseAttr.getName(); }
+  Type getType() const override { return Type::Pointwise; }
+  ErrorObject validateNode(const Context &ctx) override {
+    auto &a = pointwiseAttr;
+    const auto mode = a.getMode();
+    FUSILLI_RETURN_ERROR_IF(mode == PointwiseAttr::Mode::NOT_SET, ErrorCode::AttributeNotSet, "Pointwise mode not set");
+    const TensorPtr ins[3] = {a.getIN_0(), a.getIN_1(), a.getIN_2()};
+    const int need = PointwiseAttr::requiredInputCount(mode);
+    for (int i = 0; i < 3; ++i) {
+      const std::string nm = std::string(PointwiseAttr::modeName(mode));
+      if (i < need)
+        FUSILLI_RETURN_ERROR_IF(!ins[i], ErrorCode::AttributeNotSet,
+                                nm + " mode requires IN_" + std::to_string(i) + " input");
+      else
+        FUSILLI_RETURN_ERROR_IF(ins[i] != nullptr, ErrorCode::InvalidAttribute,
+                                nm + " mode should not have IN_" + std::to_string(i) + " input set");
+    }
+    TensorPtr out = a.getOUT_0();
+    FUSILLI_RETURN_ERROR_IF(!out, ErrorCode::AttributeNotSet, "Pointwise operation requires output");
+    if (PointwiseAttr::forcesBooleanOutput(mode)) out->setDataType(DataType::Boolean);
+    a.fillFromContext(ctx);
+    if (out->getDim().empty()) {
+      std::vector<std::vector<int64_t>> shapes;
+      for (const auto &t : ins)
+        if (t) shapes.push_back(t->getDim());
+      FUSILLI_ASSIGN_OR_RETURN(auto shape, computeBroadcastShape(shapes));
+      out->setDim(shape);
+    }
+    if (out->getStride().empty()) {
+      for (const auto &t : ins)
+        if (t && t->getDim() == out->getDim()) {
+          out->setStride(t->getStride());
+          break;
+        }
+      if (out->getStride().empty() && out->isVirtual())
+        out->setStride(generateStrideFromDim(
+            out->getDim(), generateStrideOrderPreservingFormat(ins[0]->getStride(), out->getDim().size())));
+      FUSILLI_RETURN_ERROR_IF(out->getStride().empty(), ErrorCode::InvalidAttribute,
+                              "Pointwise output strides could not be computed");
+    }
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_POINTWISE);
+    d.mode = static_cast<int32_t>(pointwiseAttr.getMode());
+    d.inputs[0] = id(pointwiseAttr.getIN_0());
+    d.inputs[1] = id(pointwiseAttr.getIN_1());
+    d.inputs[2] = id(pointwiseAttr.getIN_2());
+    d.outputs[0] = id(pointwiseAttr.getOUT_0());
+    d.fparams[0] = pointwiseAttr.getEluAlpha();
+    d.fparams[1] = pointwiseAttr.getSoftplusBeta();
+    d.fparams[2] = pointwiseAttr.getSoftplusThreshold();
+    d.fparams[3] = pointwiseAttr.getSwishBeta();
+  }
+};
+
+} // namespace fusilli
+
+#endif // FUSILLI_NODES_MORE_H

@@ -1,0 +1,161 @@
+"""Builds the C++ front-end test programs into tests/cpp/_build/.
+
+Two groups, both compiled with g++ -std=c++20 against include/ (the fusilli:: headers of this
+backend) and tests/cpp/shim/ (a single-header stand-in for Catch2 plus the `utils.h` helpers the
+reference's samples include), linked to fusilli_b200/libfusilli_b200.so:
+
+  own_*   tests/cpp/*.cpp of this repository;
+  ref_*   the reference project's sample and unit-test sources for the operators this backend
+          implements, compiled UNCHANGED from the reference checkout (directory given by
+          FUSILLI_REFERENCE_DIR, default /root/reference) when that checkout is present. Nothing
+          is copied: only the built programs land in tests/cpp/_build/.
+
+Run as `python tests/cpp/build.py [-j N] [--only PATTERN]`.
+"""
+import concurrent.futures as cf
+import fnmatch
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+OUT = os.path.join(HERE, "_build")
+REFERENCE = os.environ.get("FUSILLI_REFERENCE_DIR", "/root/reference")
+CXX = os.environ.get("FUSILLI_TEST_CXX", "/usr/bin/g++")
+
+OWN_SOURCES = ["test_frontend_host.cpp", "test_frontend_device.cpp"]
+
+# Reference programs that only need the graph API of the operators in scope. Paths are relative
+# to the reference checkout. SDPA samples there go through a user-supplied MLIR custom op and
+# batchnorm / int4 / dynamic shapes / custom ops are outside this backend, so they are not listed.
+REFERENCE_SAMPLES = [
+    "samples/convolution/conv_fprop_nchw_kcrs.cpp",
+    "samples/convolution/conv_fprop_nchw_kcrs_grouped.cpp",
+    "samples/convolution/conv_fprop_nhwc_krsc.cpp",
+    "samples/convolution/conv_fprop_nhwc_krsc_with_pad.cpp",
+    "samples/convolution/conv_fprop_with_bias.cpp",
+    "samples/convolution/conv_fprop_with_relu.cpp",
+    "samples/convolution/conv_fprop_with_relu_and_bias.cpp",
+    "samples/convolution/conv_fprop_grouped_with_relu_and_bias.cpp",
+    "samples/convolution/conv_dgrad_nhwc_krsc.cpp",
+    "samples/convolution/conv_dgrad_nhwc_krsc_grouped.cpp",
+    "samples/convolution/conv_wgrad_nhwc_krsc.cpp",
+    "samples/convolution/conv_wgrad_nhwc_krsc_grouped.cpp",
+    "samples/convolution/conv_wgrad_nhwc_krsc_grouped_strided.cpp",
+    "samples/matmul/matmul_basic.cpp",
+    "samples/matmul/matmul_basic_with_bias.cpp",
+    "samples/matmul/matmul_batched.cpp",
+    "samples/matmul/matmul_batched_with_bias.cpp",
+    "samples/pointwise/pointwise_add_transposed.cpp",
+    "samples/pointwise/pointwise_binary_cmp_ops.cpp",
+    "samples/pointwise/pointwise_binary_ops.cpp",
+    "samples/pointwise/pointwise_bwd.cpp",
+    "samples/pointwise/pointwise_scalar_mul.cpp",
+    "samples/pointwise/pointwise_ternary_ops.cpp",
+    "samples/pointwise/pointwise_unary_logical_ops.cpp",
+    "samples/pointwise/pointwise_unary_ops.cpp",
+    "samples/reduction/reduction_ops.cpp",
+    "samples/layernorm/layernorm_infer_nchw.cpp",
+    "samples/layernorm/layernorm_infer_nchw_scale_bias.cpp",
+    "samples/layernorm/layernorm_infer_nhwc_scale_bias.cpp",
+    "samples/layernorm/layernorm_train_nchw.cpp",
+    "samples/layernorm/layernorm_train_nchw_scale_bias.cpp",
+    "samples/layernorm/layernorm_train_nhwc_scale_bias.cpp",
+    "samples/rmsnorm/rmsnorm_infer_nchw.cpp",
+    "samples/rmsnorm/rmsnorm_infer_nchw_scale.cpp",
+    "samples/rmsnorm/rmsnorm_infer_nhwc_scale.cpp",
+]
+
+# Reference unit tests that need no device (attribute and node validation, context, tensors).
+REFERENCE_HOST_TESTS = [
+    "tests/test_context.cpp",
+]
+
+
+def _flags():
+    lib_dir = os.path.join(ROOT, "fusilli_b200")
+    return [
+        "-std=c++20", "-O1", "-g0", "-w",
+        "-I" + os.path.join(ROOT, "include"),
+        "-I" + os.path.join(HERE, "shim"),
+    ], ["-L" + lib_dir, "-lfusilli_b200", "-Wl,-rpath," + lib_dir,
+        "-Wl,-rpath,$ORIGIN/../../../fusilli_b200", "-s"]
+
+
+def _newer(target, deps):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(d) <= t for d in deps if os.path.exists(d))
+
+
+def _header_deps():
+    deps = []
+    for base in (os.path.join(ROOT, "include"), os.path.join(HERE, "shim")):
+        for d, _, files in os.walk(base):
+            deps += [os.path.join(d, f) for f in files]
+    deps.append(os.path.join(ROOT, "fusilli_b200", "libfusilli_b200.so"))
+    return deps
+
+
+def _compile(src, exe, extra_includes, hdeps):
+    if _newer(exe, [src] + hdeps):
+        return exe, 0, "up to date"
+    cflags, ldflags = _flags()
+    cmd = [CXX] + cflags + ["-I" + i for i in extra_includes] + [src, "-o", exe] + ldflags
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    return exe, p.returncode, p.stderr[-4000:]
+
+
+def jobs():
+    """(source, executable, extra include dirs) for everything that can be built here."""
+    out = []
+    for s in OWN_SOURCES:
+        src = os.path.join(HERE, s)
+        if os.path.exists(src):
+            out.append((src, os.path.join(OUT, "own_" + os.path.splitext(s)[0]), []))
+    if os.path.isdir(REFERENCE):
+        for rel in REFERENCE_SAMPLES + REFERENCE_HOST_TESTS:
+            src = os.path.join(REFERENCE, rel)
+            if os.path.exists(src):
+                name = os.path.splitext(os.path.basename(rel))[0]
+                out.append((src, os.path.join(OUT, "ref_" + name), [os.path.dirname(src)]))
+    return out
+
+
+def expected_programs():
+    """Names of every program the lists above describe (built or not)."""
+    own = ["own_" + os.path.splitext(s)[0] for s in OWN_SOURCES]
+    ref_dev = ["ref_" + os.path.splitext(os.path.basename(r))[0] for r in REFERENCE_SAMPLES]
+    ref_host = ["ref_" + os.path.splitext(os.path.basename(r))[0] for r in REFERENCE_HOST_TESTS]
+    return own, ref_dev, ref_host
+
+
+def build(parallel=None, only=None):
+    os.makedirs(OUT, exist_ok=True)
+    lib = os.path.join(ROOT, "fusilli_b200", "libfusilli_b200.so")
+    if not os.path.exists(lib):
+        raise RuntimeError("build fusilli_b200/libfusilli_b200.so first (python -m fusilli_b200.build)")
+    todo = [j for j in jobs() if only is None or fnmatch.fnmatch(os.path.basename(j[1]), only)]
+    hdeps = _header_deps()
+    failed = []
+    with cf.ThreadPoolExecutor(max_workers=parallel or os.cpu_count() or 4) as ex:
+        futs = [ex.submit(_compile, s, e, inc, hdeps) for s, e, inc in todo]
+        for f in cf.as_completed(futs):
+            exe, rc, msg = f.result()
+            if rc != 0:
+                failed.append((exe, msg))
+    for exe, msg in failed:
+        sys.stderr.write("FAILED %s\n%s\n" % (os.path.basename(exe), msg))
+    if failed:
+        raise RuntimeError("%d C++ test program(s) failed to build" % len(failed))
+    return [e for _, e, _ in todo]
+
+
+if __name__ in ("__main__", "__graft_build__"):
+    argv = sys.argv[1:] if __name__ == "__main__" else []
+    par = int(argv[argv.index("-j") + 1]) if "-j" in argv else None
+    pat = argv[argv.index("--only") + 1] if "--only" in argv else None
+    built = build(par, pat)
+    print("C++ front-end programs: %d in %s" % (len(built), os.path.relpath(OUT, ROOT)))

@@ -1,0 +1,2 @@
+#pragma once
+#include "../catch_test_macros.hpp"

@@ -1,0 +1,218 @@
+// Device checks of the fusilli:: C++ front end on a B200: the paths the reference's samples do
+// not reach through the graph API of this backend — SDPA as a graph node, bf16 shapes that go to
+// the tcgen05 kernels, artifact round trips into a second Graph, imported device buffers, a
+// workspace-requiring plan, and the execute() guards. Expected values are computed here on the
+// host in double precision from the same inputs.
+#include <fusilli.h>
+
+#include "utils.h"
+
+#include <catch2/catch_test_macros.hpp>
+
+#include <cmath>
+#include <cstdint>
+#include <memory>
+#include <random>
+#include <vector>
+
+using namespace fusilli;
+
+namespace {
+
+std::vector<bf16> randomBf16(size_t n, uint32_t seed, float scale) {
+  std::mt19937 rng(seed);
+  std::uniform_real_distribution<float> d(-scale, scale);
+  std::vector<bf16> v(n);
+  for (auto &x : v) x = bf16(d(rng));
+  return v;
+}
+
+std::shared_ptr<Buffer> share(Buffer &&b) { return std::make_shared<Buffer>(std::move(b)); }
+
+} // namespace
+
+TEST_CASE("bf16 batched matmul with bias runs the tensor-core plan and matches a host sum", "[matmul]") {
+  const int64_t b = 2, m = 256, k = 192, n = 384;
+  FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));
+  Graph g;
+  g.setName("cpp_matmul_bias").setIODataType(DataType::BFloat16).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto aT = g.tensor(TensorAttr().setName("a").setDim({b, m, k}).setStride({m * k, k, 1}));
+  auto bT = g.tensor(TensorAttr().setName("b").setDim({b, k, n}).setStride({k * n, n, 1}));
+  auto biasT = g.tensor(TensorAttr().setName("bias").setDim({1, 1, n}).setStride({n, n, 1}));
+  MatmulAttr mm;
+  mm.setName("mm");
+  auto cT = g.matmul(aT, bT, mm);
+  PointwiseAttr add;
+  add.setName("add").setMode(PointwiseAttr::Mode::ADD);
+  auto yT = g.pointwise(cT, biasT, add);
+  yT->setOutput(true);
+  FUSILLI_REQUIRE_OK(g.validate());
+  FUSILLI_REQUIRE_OK(g.compile(handle, /*remove=*/true));
+  FUSILLI_REQUIRE_ASSIGN(auto stats, g.readCompilationCacheFile(CachedAssetsType::Statistics));
+  REQUIRE(stats.find("gemm_tcgen05") != std::string::npos);
+
+  auto a = randomBf16(b * m * k, 1, 1.f), bb = randomBf16(b * k * n, 2, 1.f), bias = randomBf16(n, 3, 1.f);
+  FUSILLI_REQUIRE_ASSIGN(auto aBuf, allocateBufferOfType(handle, aT, a));
+  FUSILLI_REQUIRE_ASSIGN(auto bBuf, allocateBufferOfType(handle, bT, bb));
+  FUSILLI_REQUIRE_ASSIGN(auto biasBuf, allocateBufferOfType(handle, biasT, bias));
+  FUSILLI_REQUIRE_ASSIGN(auto yBuf, allocateBufferOfType(handle, yT, DataType::BFloat16, 0.0));
+  FUSILLI_REQUIRE_ASSIGN(auto ws, g.getWorkspaceSize());
+  FUSILLI_REQUIRE_ASSIGN(auto wsBuf, allocateWorkspace(handle, ws));
+  Graph::VariantPack pack = {{aT, aBuf}, {bT, bBuf}, {biasT, biasBuf}, {yT, yBuf}};
+  FUSILLI_REQUIRE_OK(g.execute(handle, pack, wsBuf));
+  std::vector<bf16> y;
+  FUSILLI_REQUIRE_OK(yBuf->read(handle, y));
+  double worst = 0;
+  for (int64_t bi = 0; bi < b; ++bi)
+    for (int64_t i = 0; i < m; i += 7)
+      for (int64_t j = 0; j < n; j += 5) {
+        double acc = float(bias[j]);
+        for (int64_t kk = 0; kk < k; ++kk) acc += double(float(a[(bi * m + i) * k + kk])) * double(float(bb[(bi * k + kk) * n + j]));
+        const double got = float(y[(bi * m + i) * n + j]);
+        worst = std::max(worst, std::abs(got - acc) / (1.0 + std::abs(acc)));
+      }
+  INFO("worst relative error " << worst);
+  REQUIRE(worst < 1.0 / 128); // one bf16 rounding of the result
+}
+
+TEST_CASE("SDPA graph node: causal attention matches a host softmax", "[sdpa]") {
+  const int64_t b = 1, h = 2, s = 256, d = 128;
+  FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));
+  Graph g;
+  g.setName("cpp_sdpa_causal").setIODataType(DataType::BFloat16).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto mk = [&](const char *name) {
+    return g.tensor(TensorAttr().setName(name).setDim({b, h, s, d}).setStride({h * s * d, s * d, d, 1}));
+  };
+  auto qT = mk("q"), kT = mk("k"), vT = mk("v");
+  SdpaAttr attr;
+  attr.setName("attn").setIsCausal(true);
+  auto oT = g.sdpa(qT, kT, vT, nullptr, attr);
+  oT->setOutput(true);
+  FUSILLI_REQUIRE_OK(g.validate());
+  FUSILLI_REQUIRE_OK(g.compile(handle, /*remove=*/true));
+  auto q = randomBf16(b * h * s * d, 11, 1.f), k = randomBf16(b * h * s * d, 12, 1.f), v = randomBf16(b * h * s * d, 13, 1.f);
+  FUSILLI_REQUIRE_ASSIGN(auto qBuf, allocateBufferOfType(handle, qT, q));
+  FUSILLI_REQUIRE_ASSIGN(auto kBuf, allocateBufferOfType(handle, kT, k));
+  FUSILLI_REQUIRE_ASSIGN(auto vBuf, allocateBufferOfType(handle, vT, v));
+  FUSILLI_REQUIRE_ASSIGN(auto oBuf, allocateBufferOfType(handle, oT, DataType::BFloat16, 0.0));
+  FUSILLI_REQUIRE_ASSIGN(auto ws, g.getWorkspaceSize());
+  FUSILLI_REQUIRE_ASSIGN(auto wsBuf, allocateWorkspace(handle, ws));
+  Graph::VariantPack pack = {{qT, qBuf}, {kT, kBuf}, {vT, vBuf}, {oT, oBuf}};
+  FUSILLI_REQUIRE_OK(g.execute(handle, pack, wsBuf));
+  std::vector<bf16> o;
+  FUSILLI_REQUIRE_OK(oBuf->read(handle, o));
+  const double scale = 1.0 / std::sqrt(double(d));
+  double worst = 0;
+  for (int64_t hh = 0; hh < h; ++hh)
+    for (int64_t i = 0; i < s; i += 17) {
+      std::vector<double> p(i + 1);
+      double mx = -1e300, sum = 0;
+      for (int64_t j = 0; j <= i; ++j) {
+        double acc = 0;
+        for (int64_t t = 0; t < d; ++t) acc += double(float(q[(hh * s + i) * d + t])) * double(float(k[(hh * s + j) * d + t]));
+        p[j] = acc * scale;
+        mx = std::max(mx, p[j]);
+      }
+      for (auto &x : p) { x = std::exp(x - mx); sum += x; }
+      for (int64_t t = 0; t < d; t += 9) {
+        double acc = 0;
+        for (int64_t j = 0; j <= i; ++j) acc += p[j] * double(float(v[(hh * s + j) * d + t]));
+        acc /= sum;
+        worst = std::max(worst, std::abs(double(float(o[(hh * s + i) * d + t])) - acc));
+      }
+    }
+  INFO("worst absolute error " << worst);
+  REQUIRE(worst < 2e-2);
+}
+
+TEST_CASE("artifact built without a device loads into a second graph and an imported buffer", "[artifact]") {
+  const int64_t n = 4, c = 32, hw = 16, kk = 64;
+  auto build = [&](Graph &g) {
+    g.setName("cpp_conv_artifact").setIODataType(DataType::BFloat16).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+    auto x = g.tensor(TensorAttr().setName("x").setDim({n, c, hw, hw}).setStride({c * hw * hw, 1, c * hw, c}));
+    auto w = g.tensor(TensorAttr().setName("w").setDim({kk, c, 3, 3}).setStride({c * 9, 1, c * 3, c}));
+    ConvFPropAttr conv;
+    conv.setName("conv").setPadding({1, 1}).setStride({1, 1}).setDilation({1, 1});
+    auto y = g.convFProp(x, w, conv);
+    PointwiseAttr relu;
+    relu.setName("relu").setMode(PointwiseAttr::Mode::RELU_FWD);
+    auto z = g.pointwise(y, relu);
+    z->setOutput(true);
+    return std::make_tuple(x, w, z);
+  };
+  Graph offline;
+  build(offline);
+  FUSILLI_REQUIRE_OK(offline.validate());
+  FUSILLI_REQUIRE_ASSIGN(auto bytes, offline.compileToArtifact(Backend::CUDA, /*remove=*/true));
+
+  FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));
+  Graph online;
+  auto [xT, wT, zT] = build(online);
+  auto notValidated = online.loadFromArtifact(handle, bytes);
+  REQUIRE(notValidated.getCode() == ErrorCode::NotValidated);
+  FUSILLI_REQUIRE_OK(online.validate());
+  FUSILLI_REQUIRE_OK(online.loadFromArtifact(handle, bytes));
+
+  // all-ones input and filter: interior outputs are 9*c, corners 4*c
+  FUSILLI_REQUIRE_ASSIGN(auto xBuf, allocateBufferOfType(handle, xT, DataType::BFloat16, 1.0));
+  FUSILLI_REQUIRE_ASSIGN(auto wBuf, allocateBufferOfType(handle, wT, DataType::BFloat16, 1.0));
+  FUSILLI_REQUIRE_ASSIGN(auto owned, Buffer::allocateRaw(handle, size_t(n * kk * hw * hw) * sizeof(bf16)));
+  // the output goes through an import of the raw device pointer, as an integration would do
+  FUSILLI_REQUIRE_ASSIGN(auto imported, Buffer::import(handle, owned.devicePointer(), owned.sizeInBytes()));
+  auto zBuf = share(std::move(imported));
+  Graph::VariantPack pack = {{xT, xBuf}, {wT, wBuf}, {zT, zBuf}};
+
+  // execute() before getWorkspaceSize() is refused, as in the reference
+  auto early = online.execute(handle, pack, nullptr);
+  REQUIRE(early.getCode() == ErrorCode::InvalidArgument);
+  FUSILLI_REQUIRE_ASSIGN(auto ws, online.getWorkspaceSize());
+  FUSILLI_REQUIRE_ASSIGN(auto wsBuf, allocateWorkspace(handle, ws));
+  FUSILLI_REQUIRE_OK(online.execute(handle, pack, wsBuf));
+  std::vector<bf16> z;
+  FUSILLI_REQUIRE_OK(owned.read(handle, z));
+  REQUIRE(z.size() == size_t(n * kk * hw * hw));
+  auto at = [&](int64_t ni, int64_t ki, int64_t y, int64_t x) { return float(z[((ni * hw + y) * hw + x) * kk + ki]); };
+  REQUIRE(at(0, 0, 0, 0) == 4.f * c);
+  REQUIRE(at(1, 5, 0, 7) == 6.f * c);
+  REQUIRE(at(3, 63, 8, 8) == 9.f * c);
+  REQUIRE(at(2, 17, 15, 15) == 4.f * c);
+
+  // a missing tensor in the variant pack is an error, not a crash
+  Graph::VariantPack partial = {{xT, xBuf}, {zT, zBuf}};
+  auto missing = online.execute(handle, partial, wsBuf);
+  REQUIRE(missing.getCode() == ErrorCode::VariantPackError);
+}
+
+TEST_CASE("conv wgrad plan asks for a workspace and refuses to run without it", "[wgrad]") {
+  const int64_t n = 8, c = 64, hw = 16, kk = 64;
+  FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));
+  Graph g;
+  g.setName("cpp_wgrad_workspace").setIODataType(DataType::BFloat16).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto dyT = g.tensor(TensorAttr().setName("dy").setDim({n, kk, hw, hw}).setStride({kk * hw * hw, 1, kk * hw, kk}));
+  auto xT = g.tensor(TensorAttr().setName("x").setDim({n, c, hw, hw}).setStride({c * hw * hw, 1, c * hw, c}));
+  ConvWGradAttr attr;
+  attr.setName("wgrad").setPadding({1, 1}).setStride({1, 1}).setDilation({1, 1});
+  auto dwT = g.convWGrad(dyT, xT, attr);
+  dwT->setOutput(true).setDim({kk, c, 3, 3}).setStride({c * 9, 1, c * 3, c});
+  FUSILLI_REQUIRE_OK(g.validate());
+  FUSILLI_REQUIRE_OK(g.compile(handle, /*remove=*/true));
+  FUSILLI_REQUIRE_ASSIGN(auto ws, g.getWorkspaceSize());
+  REQUIRE(ws.has_value());
+  FUSILLI_REQUIRE_ASSIGN(auto dyBuf, allocateBufferOfType(handle, dyT, DataType::BFloat16, 1.0));
+  FUSILLI_REQUIRE_ASSIGN(auto xBuf, allocateBufferOfType(handle, xT, DataType::BFloat16, 1.0));
+  FUSILLI_REQUIRE_ASSIGN(auto dwBuf, allocateBufferOfType(handle, dwT, DataType::BFloat16, 0.0));
+  Graph::VariantPack pack = {{dyT, dyBuf}, {xT, xBuf}, {dwT, dwBuf}};
+  if (*ws > 0) {
+    auto refused = g.execute(handle, pack, nullptr);
+    REQUIRE(refused.getCode() == ErrorCode::InvalidArgument);
+  }
+  FUSILLI_REQUIRE_ASSIGN(auto wsBuf, allocateWorkspace(handle, ws));
+  FUSILLI_REQUIRE_OK(g.execute(handle, pack, wsBuf));
+  std::vector<bf16> dw;
+  FUSILLI_REQUIRE_OK(dwBuf->read(handle, dw));
+  // all-ones dy and x: the centre tap sums every pixel of every image, a corner tap (hw-1)^2
+  auto at = [&](int64_t ki, int64_t ci, int64_t r, int64_t s) { return float(dw[((ki * 3 + r) * 3 + s) * c + ci]); };
+  REQUIRE(at(0, 0, 1, 1) == float(n * hw * hw));
+  REQUIRE(at(63, 63, 0, 0) == float(n * (hw - 1) * (hw - 1)));
+  REQUIRE(at(5, 9, 1, 0) == float(n * hw * (hw - 1)));
+}

@@ -1,6 +1,6 @@
 // Per-op attribute bags of the graph builders: same class names, setters and getters as the
 // reference's include/fusilli/attributes/{conv,matmul,sdpa,layernorm,rmsnorm,reduction,
-// pointwise}_attributes.h. Tensors are held in fixed slots (an array per bag) rather than maps.
+// pointwise}_attributes.h. 
 #ifndef FUSILLI_ATTRIBUTES_H
 #define FUSILLI_ATTRIBUTES_H
 
@@ -20,37 +20,65 @@ using TensorPtr = std::shared_ptr<TensorAttr>;
 
 enum class NormFwdPhase : uint8_t { NOT_SET, TRAINING, INFERENCE };
 
-// Common part of every bag: name, compute type, NIN input slots, NOUT output slots.
-template <typename Derived, int NIN, int NOUT> class AttrBase {
+// Common part of every bag (reference attributes/attributes.h:30-126): name, compute type, and
+// tensors kept in the derived class's `inputs` / `outputs` maps, keyed by its InputNames /
+// OutputNames enums.
+template <typename Derived> class AttributesCRTP {
 public:
   DataType computeDataType = DataType::NotSet;
   const std::string &getName() const { return name_; }
   Derived &setName(const std::string &n) { name_ = n; return self(); }
   Derived &setComputeDataType(DataType t) { computeDataType = t; return self(); }
 
+  template <typename K> Derived &setInput(const K &key, const TensorPtr &t) {
+    self().inputs[key] = t;
+    return self();
+  }
+  template <typename K> Derived &setOutput(const K &key, const TensorPtr &t) {
+    self().outputs[key] = t;
+    return self();
+  }
+  template <typename K> TensorPtr getInput(const K &key) const {
+    auto it = self().inputs.find(key);
+    return it == self().inputs.end() ? nullptr : it->second;
+  }
+  template <typename K> TensorPtr getOutput(const K &key) const {
+    auto it = self().outputs.find(key);
+    return it == self().outputs.end() ? nullptr : it->second;
+  }
+
+  // Unset compute type and unset tensor dtypes take the graph context's defaults.
   void fillFromContext(const Context &ctx) {
     if (computeDataType == DataType::NotSet) computeDataType = ctx.getComputeDataType();
-    for (auto &t : in_) if (t) t->fillFromContext(ctx);
-    for (auto &t : out_) if (t) t->fillFromContext(ctx);
+    for (auto &kv : self().inputs)
+      if (kv.second) kv.second->fillFromContext(ctx);
+    for (auto &kv : self().outputs)
+      if (kv.second) kv.second->fillFromContext(ctx);
   }
-  const std::array<TensorPtr, NIN> &inputSlots() const { return in_; }
-  const std::array<TensorPtr, NOUT> &outputSlots() const { return out_; }
 
 protected:
   Derived &self() { return static_cast<Derived &>(*this); }
-  std::array<TensorPtr, NIN> in_{};
-  std::array<TensorPtr, NOUT> out_{};
+  const Derived &self() const { return static_cast<const Derived &>(*this); }
   std::string name_;
 };
 
-#define FUSILLI_SLOT(CLASS, ARR, IDX, NAME)                                                          \
-  CLASS &set##NAME(const TensorPtr &t) { ARR[IDX] = t; return *this; }                               \
-  TensorPtr get##NAME() const { return ARR[IDX]; }
+#define FUSILLI_TENSOR_MAPS                                                                          \
+  std::unordered_map<InputNames, TensorPtr> inputs;                                                  \
+  std::unordered_map<OutputNames, TensorPtr> outputs;
+#define FUSILLI_IN(CLASS, KEY, NAME)                                                                 \
+  CLASS &set##NAME(const TensorPtr &t) { return setInput(InputNames::KEY, t); }                      \
+  TensorPtr get##NAME() const { return getInput(InputNames::KEY); }
+#define FUSILLI_OUT(CLASS, KEY, NAME)                                                                \
+  CLASS &set##NAME(const TensorPtr &t) { return setOutput(OutputNames::KEY, t); }                    \
+  TensorPtr get##NAME() const { return getOutput(OutputNames::KEY); }
 
 #define FUSILLI_CONV_GEOMETRY(CLASS)                                                                 \
   CLASS &setPadding(const std::vector<int64_t> &v) { padding_ = v; return *this; }                  \
   CLASS &setStride(const std::vector<int64_t> &v) { stride_ = v; return *this; }                    \
   CLASS &setDilation(const std::vector<int64_t> &v) { dilation_ = v; return *this; }                \
+  template <Int64Range R> CLASS &setPadding(R &&v) { padding_.assign(v.begin(), v.end()); return *this; }  \
+  template <Int64Range R> CLASS &setStride(R &&v) { stride_.assign(v.begin(), v.end()); return *this; }    \
+  template <Int64Range R> CLASS &setDilation(R &&v) { dilation_.assign(v.begin(), v.end()); return *this; } \
   const std::vector<int64_t> &getPadding() const { return padding_; }                               \
   const std::vector<int64_t> &getStride() const { return stride_; }                                 \
   const std::vector<int64_t> &getDilation() const { return dilation_; }                             \
@@ -60,44 +88,59 @@ private:                                                                        
                                                                                                      \
 public:
 
-class ConvFPropAttr : public AttrBase<ConvFPropAttr, 2, 1> {
+class ConvFPropAttr : public AttributesCRTP<ConvFPropAttr> {
 public:
-  FUSILLI_SLOT(ConvFPropAttr, in_, 0, X)
-  FUSILLI_SLOT(ConvFPropAttr, in_, 1, W)
-  FUSILLI_SLOT(ConvFPropAttr, out_, 0, Y)
+  enum class InputNames : uint8_t { X, W };
+  enum class OutputNames : uint8_t { Y };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(ConvFPropAttr, X, X)
+  FUSILLI_IN(ConvFPropAttr, W, W)
+  FUSILLI_OUT(ConvFPropAttr, Y, Y)
   FUSILLI_CONV_GEOMETRY(ConvFPropAttr)
 };
 
-class ConvWGradAttr : public AttrBase<ConvWGradAttr, 2, 1> {
+class ConvWGradAttr : public AttributesCRTP<ConvWGradAttr> {
 public:
-  FUSILLI_SLOT(ConvWGradAttr, in_, 0, DY)
-  FUSILLI_SLOT(ConvWGradAttr, in_, 1, X)
-  FUSILLI_SLOT(ConvWGradAttr, out_, 0, DW)
+  enum class InputNames : uint8_t { DY, X };
+  enum class OutputNames : uint8_t { DW };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(ConvWGradAttr, DY, DY)
+  FUSILLI_IN(ConvWGradAttr, X, X)
+  FUSILLI_OUT(ConvWGradAttr, DW, DW)
   FUSILLI_CONV_GEOMETRY(ConvWGradAttr)
 };
 
-class ConvDGradAttr : public AttrBase<ConvDGradAttr, 2, 1> {
+class ConvDGradAttr : public AttributesCRTP<ConvDGradAttr> {
 public:
-  FUSILLI_SLOT(ConvDGradAttr, in_, 0, DY)
-  FUSILLI_SLOT(ConvDGradAttr, in_, 1, W)
-  FUSILLI_SLOT(ConvDGradAttr, out_, 0, DX)
+  enum class InputNames : uint8_t { DY, W };
+  enum class OutputNames : uint8_t { DX };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(ConvDGradAttr, DY, DY)
+  FUSILLI_IN(ConvDGradAttr, W, W)
+  FUSILLI_OUT(ConvDGradAttr, DX, DX)
   FUSILLI_CONV_GEOMETRY(ConvDGradAttr)
 };
 
-class MatmulAttr : public AttrBase<MatmulAttr, 2, 1> {
+class MatmulAttr : public AttributesCRTP<MatmulAttr> {
 public:
-  FUSILLI_SLOT(MatmulAttr, in_, 0, A)
-  FUSILLI_SLOT(MatmulAttr, in_, 1, B)
-  FUSILLI_SLOT(MatmulAttr, out_, 0, C)
+  enum class InputNames : uint8_t { A, B };
+  enum class OutputNames : uint8_t { C };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(MatmulAttr, A, A)
+  FUSILLI_IN(MatmulAttr, B, B)
+  FUSILLI_OUT(MatmulAttr, C, C)
 };
 
-class SdpaAttr : public AttrBase<SdpaAttr, 4, 1> {
+class SdpaAttr : public AttributesCRTP<SdpaAttr> {
 public:
-  FUSILLI_SLOT(SdpaAttr, in_, 0, Q)
-  FUSILLI_SLOT(SdpaAttr, in_, 1, K)
-  FUSILLI_SLOT(SdpaAttr, in_, 2, V)
-  FUSILLI_SLOT(SdpaAttr, in_, 3, MASK)
-  FUSILLI_SLOT(SdpaAttr, out_, 0, O)
+  enum class InputNames : uint8_t { Q, K, V, MASK };
+  enum class OutputNames : uint8_t { O };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(SdpaAttr, Q, Q)
+  FUSILLI_IN(SdpaAttr, K, K)
+  FUSILLI_IN(SdpaAttr, V, V)
+  FUSILLI_IN(SdpaAttr, MASK, MASK)
+  FUSILLI_OUT(SdpaAttr, O, O)
   SdpaAttr &setDropout(float p) { dropout_ = p; return *this; }
   SdpaAttr &setIsCausal(bool v) { causal_ = v; return *this; }
   SdpaAttr &setScale(std::optional<float> s) { scale_ = s; return *this; }
@@ -113,15 +156,18 @@ private:
   std::optional<float> scale_;
 };
 
-class LayernormAttr : public AttrBase<LayernormAttr, 4, 3> {
+class LayernormAttr : public AttributesCRTP<LayernormAttr> {
 public:
-  FUSILLI_SLOT(LayernormAttr, in_, 0, X)
-  FUSILLI_SLOT(LayernormAttr, in_, 1, SCALE)
-  FUSILLI_SLOT(LayernormAttr, in_, 2, BIAS)
-  FUSILLI_SLOT(LayernormAttr, in_, 3, Epsilon)
-  FUSILLI_SLOT(LayernormAttr, out_, 0, Y)
-  FUSILLI_SLOT(LayernormAttr, out_, 1, MEAN)
-  FUSILLI_SLOT(LayernormAttr, out_, 2, INV_VARIANCE)
+  enum class InputNames : uint8_t { X, SCALE, BIAS, EPSILON };
+  enum class OutputNames : uint8_t { Y, MEAN, INV_VARIANCE };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(LayernormAttr, X, X)
+  FUSILLI_IN(LayernormAttr, SCALE, SCALE)
+  FUSILLI_IN(LayernormAttr, BIAS, BIAS)
+  FUSILLI_IN(LayernormAttr, EPSILON, Epsilon)
+  FUSILLI_OUT(LayernormAttr, Y, Y)
+  FUSILLI_OUT(LayernormAttr, MEAN, MEAN)
+  FUSILLI_OUT(LayernormAttr, INV_VARIANCE, INV_VARIANCE)
   LayernormAttr &setForwardPhase(NormFwdPhase p) { phase_ = p; return *this; }
   NormFwdPhase getForwardPhase() const { return phase_; }
 
@@ -129,13 +175,16 @@ private:
   NormFwdPhase phase_ = NormFwdPhase::NOT_SET;
 };
 
-class RmsnormAttr : public AttrBase<RmsnormAttr, 3, 2> {
+class RmsnormAttr : public AttributesCRTP<RmsnormAttr> {
 public:
-  FUSILLI_SLOT(RmsnormAttr, in_, 0, X)
-  FUSILLI_SLOT(RmsnormAttr, in_, 1, SCALE)
-  FUSILLI_SLOT(RmsnormAttr, in_, 2, Epsilon)
-  FUSILLI_SLOT(RmsnormAttr, out_, 0, Y)
-  FUSILLI_SLOT(RmsnormAttr, out_, 1, INV_RMS)
+  enum class InputNames : uint8_t { X, SCALE, EPSILON };
+  enum class OutputNames : uint8_t { Y, INV_RMS };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(RmsnormAttr, X, X)
+  FUSILLI_IN(RmsnormAttr, SCALE, SCALE)
+  FUSILLI_IN(RmsnormAttr, EPSILON, Epsilon)
+  FUSILLI_OUT(RmsnormAttr, Y, Y)
+  FUSILLI_OUT(RmsnormAttr, INV_RMS, INV_RMS)
   RmsnormAttr &setForwardPhase(NormFwdPhase p) { phase_ = p; return *this; }
   NormFwdPhase getForwardPhase() const { return phase_; }
 
@@ -143,12 +192,15 @@ private:
   NormFwdPhase phase_ = NormFwdPhase::NOT_SET;
 };
 
-class ReductionAttr : public AttrBase<ReductionAttr, 1, 1> {
+class ReductionAttr : public AttributesCRTP<ReductionAttr> {
 public:
+  enum class InputNames : uint8_t { X };
+  enum class OutputNames : uint8_t { Y };
+  FUSILLI_TENSOR_MAPS
   // Same order as the C ABI's FB_RED_* values.
   enum class Mode : uint8_t { NOT_SET, ADD, SUM, MUL, MIN, MAX, AMAX, AVG, NORM1, NORM2, MUL_NO_ZEROS };
-  FUSILLI_SLOT(ReductionAttr, in_, 0, X)
-  FUSILLI_SLOT(ReductionAttr, out_, 0, Y)
+  FUSILLI_IN(ReductionAttr, X, X)
+  FUSILLI_OUT(ReductionAttr, Y, Y)
   ReductionAttr &setMode(Mode m) { mode_ = m; return *this; }
   Mode getMode() const { return mode_; }
   static const char *modeName(Mode m) {
@@ -163,8 +215,11 @@ private:
   Mode mode_ = Mode::NOT_SET;
 };
 
-class PointwiseAttr : public AttrBase<PointwiseAttr, 3, 1> {
+class PointwiseAttr : public AttributesCRTP<PointwiseAttr> {
 public:
+  enum class InputNames : uint8_t { IN_0, IN_1, IN_2 };
+  enum class OutputNames : uint8_t { OUT_0 };
+  FUSILLI_TENSOR_MAPS
   // Same order as the C ABI's FB_PW_* values.
   enum class Mode : uint8_t {
     NOT_SET, ABS, ADD, ADD_SQUARE, BINARY_SELECT, CEIL, CMP_EQ, CMP_GE, CMP_GT, CMP_LE, CMP_LT, CMP_NEQ, DIV,
@@ -172,10 +227,10 @@ public:
     LOGICAL_AND, LOGICAL_NOT, LOGICAL_OR, MAX_OP, MIN_OP, MUL, NEG, RECIPROCAL, RELU_BWD, RELU_FWD, RSQRT,
     SIGMOID_FWD, SIN, SOFTPLUS_FWD, SQRT, SUB, SWISH_BWD, SWISH_FWD, TAN, TANH_BWD, TANH_FWD
   };
-  FUSILLI_SLOT(PointwiseAttr, in_, 0, IN_0)
-  FUSILLI_SLOT(PointwiseAttr, in_, 1, IN_1)
-  FUSILLI_SLOT(PointwiseAttr, in_, 2, IN_2)
-  FUSILLI_SLOT(PointwiseAttr, out_, 0, OUT_0)
+  FUSILLI_IN(PointwiseAttr, IN_0, IN_0)
+  FUSILLI_IN(PointwiseAttr, IN_1, IN_1)
+  FUSILLI_IN(PointwiseAttr, IN_2, IN_2)
+  FUSILLI_OUT(PointwiseAttr, OUT_0, OUT_0)
   PointwiseAttr &setMode(Mode m) { mode_ = m; return *this; }
   PointwiseAttr &setEluAlpha(float v) { eluAlpha_ = v; return *this; }
   PointwiseAttr &setSoftplusBeta(float v) { softplusBeta_ = v; return *this; }
@@ -240,7 +295,9 @@ inline const std::unordered_map<ReductionAttr::Mode, std::string> ReductionAttr:
 static_assert(static_cast<int>(PointwiseAttr::Mode::TANH_FWD) == FB_PW_TANH_FWD, "pointwise modes out of step with the C ABI");
 static_assert(static_cast<int>(ReductionAttr::Mode::MUL_NO_ZEROS) == FB_RED_MUL_NO_ZEROS, "reduction modes out of step with the C ABI");
 
-#undef FUSILLI_SLOT
+#undef FUSILLI_IN
+#undef FUSILLI_OUT
+#undef FUSILLI_TENSOR_MAPS
 #undef FUSILLI_CONV_GEOMETRY
 
 } // namespace fusilli

@@ -65,6 +65,13 @@ public:
     FUSILLI_RETURN_ERROR_IF(!f.is_open(), ErrorCode::FileSystemFailure, "Failed to create file: " + path.string());
     return ok(CacheFile(path, remove));
   }
+  // An existing cache file; never removed by this object.
+  static ErrorOr<CacheFile> open(const std::string &graphName, const std::string &fileName) {
+    const auto path = getPath(graphName, fileName);
+    FUSILLI_RETURN_ERROR_IF(!std::filesystem::exists(path), ErrorCode::FileSystemFailure,
+                            "File does not exist: " + path.string());
+    return ok(CacheFile(path, false));
+  }
   ErrorObject write(const std::string &content) {
     std::ofstream f(path, std::ios::out | std::ios::binary);
     FUSILLI_RETURN_ERROR_IF(!f.is_open(), ErrorCode::FileSystemFailure, "Failed to open file: " + path.string());
@@ -166,28 +173,28 @@ public:
     autoName(a, "conv_fprop", {{"X", x}, {"W", w}});
     auto y = outputTensor(a.getName() + "_Y");
     a.setX(x).setW(w).setY(y);
-    nodes_.push_back(std::make_unique<ConvFPropNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<ConvFPropNode>(std::move(a), context));
     return y;
   }
   TensorPtr convWGrad(const TensorPtr &dy, const TensorPtr &x, ConvWGradAttr &a) {
     autoName(a, "conv_wgrad", {{"DY", dy}, {"X", x}});
     auto dw = outputTensor(a.getName() + "_DW");
     a.setDY(dy).setX(x).setDW(dw);
-    nodes_.push_back(std::make_unique<ConvWGradNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<ConvWGradNode>(std::move(a), context));
     return dw;
   }
   TensorPtr convDGrad(const TensorPtr &dy, const TensorPtr &w, ConvDGradAttr &a) {
     autoName(a, "conv_dgrad", {{"DY", dy}, {"W", w}});
     auto dx = outputTensor(a.getName() + "_DX");
     a.setDY(dy).setW(w).setDX(dx);
-    nodes_.push_back(std::make_unique<ConvDGradNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<ConvDGradNode>(std::move(a), context));
     return dx;
   }
   TensorPtr matmul(const TensorPtr &a_, const TensorPtr &b, MatmulAttr &a) {
     autoName(a, "matmul", {{"A", a_}, {"B", b}});
     auto c = outputTensor(a.getName() + "_C");
     a.setA(a_).setB(b).setC(c);
-    nodes_.push_back(std::make_unique<MatmulNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<MatmulNode>(std::move(a), context));
     return c;
   }
   TensorPtr sdpa(const TensorPtr &q, const TensorPtr &k, const TensorPtr &v, const TensorPtr &mask, SdpaAttr &a) {
@@ -195,7 +202,7 @@ public:
     auto o = outputTensor(a.getName() + "_O");
     a.setQ(q).setK(k).setV(v).setO(o);
     if (mask) a.setMASK(mask);
-    nodes_.push_back(std::make_unique<SdpaNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<SdpaNode>(std::move(a), context));
     return o;
   }
   std::array<TensorPtr, 3> layernorm(const TensorPtr &x, const TensorPtr &scale, const TensorPtr &bias,
@@ -208,7 +215,7 @@ public:
       v = outputTensor(a.getName() + "_INV_VARIANCE");
     }
     a.setX(x).setSCALE(scale).setBIAS(bias).setY(y).setMEAN(m).setINV_VARIANCE(v);
-    nodes_.push_back(std::make_unique<LayerNormNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<LayerNormNode>(std::move(a), context));
     return {y, m, v};
   }
   std::array<TensorPtr, 2> rmsnorm(const TensorPtr &x, const TensorPtr &scale, RmsnormAttr &a) {
@@ -217,14 +224,14 @@ public:
     TensorPtr r;
     if (a.getForwardPhase() == NormFwdPhase::TRAINING) r = outputTensor(a.getName() + "_INV_RMS");
     a.setX(x).setSCALE(scale).setY(y).setINV_RMS(r);
-    nodes_.push_back(std::make_unique<RmsNormNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<RmsNormNode>(std::move(a), context));
     return {y, r};
   }
   TensorPtr reduction(const TensorPtr &x, ReductionAttr &a) {
     autoName(a, "reduction", {{"X", x}});
     auto y = outputTensor(a.getName() + "_Y");
     a.setX(x).setY(y);
-    nodes_.push_back(std::make_unique<ReductionNode>(std::move(a)));
+    nodes_.push_back(std::make_unique<ReductionNode>(std::move(a), context));
     return y;
   }
   TensorPtr pointwise(const TensorPtr &in0, PointwiseAttr &a) { return addPointwise({in0, nullptr, nullptr}, 1, a); }

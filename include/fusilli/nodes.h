@@ -46,12 +46,31 @@ public:
   enum class Type : uint8_t { Composite, Convolution, Pointwise, WGrad, DGrad, LayerNorm, BatchNorm, RmsNorm,
                               Matmul, Reduction, Custom, Sdpa };
   using TensorId = std::function<int32_t(const TensorPtr &)>;
+  // A node keeps its own copy of the graph context as it was when the node was added
+  // (reference node.h:47).
+  explicit INode(const Context &ctx) : context(ctx) {}
   virtual ~INode() = default;
   virtual const std::string &getName() const = 0;
   virtual Type getType() const = 0;
-  // pre-validation, inference of unset dims/strides/dtypes, post-validation
-  virtual ErrorObject validateNode(const Context &ctx) = 0;
-  virtual void describe(fb_node_desc &d, const TensorId &id) const = 0;
+  Context context;
+
+  // Three phases, as in the reference (node.h:63-65): checks that need only what the user set,
+  // inference of unset dims / strides / dtypes, checks on the completed node.
+  virtual ErrorObject preValidateNode() const { return ok(); }
+  virtual ErrorObject inferPropertiesNode() = 0;
+  virtual ErrorObject postValidateNode() const { return ok(); }
+  ErrorObject validateNode() {
+    FUSILLI_CHECK_ERROR(preValidateNode());
+    FUSILLI_CHECK_ERROR(inferPropertiesNode());
+    FUSILLI_CHECK_ERROR(postValidateNode());
+    return ok();
+  }
+  // Writes the node into the C ABI's POD descriptor; op = -1 marks a node kind the B200 backend
+  // cannot run, which fb_plan_build rejects.
+  virtual void describe(fb_node_desc &d, const TensorId &) const {
+    std::memset(&d, 0, sizeof(d));
+    d.op = -1;
+  }
 };
 
 namespace detail {
@@ -78,11 +97,13 @@ template <typename A> void convGeometry(fb_node_desc &d, const A &a) {
     d.dilation[i] = a.getDilation()[i];
   }
 }
-template <typename A>
-ErrorObject checkConvGeometry(const std::string &who, const A &a, size_t rank) {
+template <typename A> ErrorObject checkConvGeometrySet(const std::string &who, const A &a) {
   FUSILLI_RETURN_ERROR_IF(a.getPadding().empty(), ErrorCode::AttributeNotSet, who + " padding not set");
   FUSILLI_RETURN_ERROR_IF(a.getStride().empty(), ErrorCode::AttributeNotSet, who + " stride not set");
   FUSILLI_RETURN_ERROR_IF(a.getDilation().empty(), ErrorCode::AttributeNotSet, who + " dilation not set");
+  return ok();
+}
+template <typename A> ErrorObject checkConvGeometryRank(const std::string &who, const A &a, size_t rank) {
   const size_t ns = rank - 2;
   FUSILLI_RETURN_ERROR_IF(a.getPadding().size() != ns, ErrorCode::InvalidAttribute,
                           who + " padding size does not match number of spatial dimensions");
@@ -92,15 +113,22 @@ ErrorObject checkConvGeometry(const std::string &who, const A &a, size_t rank) {
                           who + " dilation size does not match number of spatial dimensions");
   return ok();
 }
-inline ErrorObject checkGroups(const std::string &who, int64_t inC, int64_t outC, int64_t filterC) {
+// `inName` / `outName` are how the message names the two channel counts.
+inline ErrorObject checkGroups(const std::string &who, const std::string &inName, const std::string &outName,
+                               int64_t inC, int64_t outC, int64_t filterC) {
   FUSILLI_RETURN_ERROR_IF(filterC <= 0 || inC % filterC != 0, ErrorCode::InvalidAttribute,
-                          who + " input channels must be divisible by the filter channels");
+                          who + " " + inName + " channels must be divisible by the filter" +
+                              (inName == "input" ? "" : " (W)") + " channels");
   const int64_t groups = inC / filterC;
   FUSILLI_RETURN_ERROR_IF(groups <= 0 || groups > inC || groups > outC, ErrorCode::InvalidAttribute,
                           who + " group count must be greater than 0 and less than or equal to the "
                                 "numbers of input and outputs channels");
   FUSILLI_RETURN_ERROR_IF(outC % groups != 0, ErrorCode::InvalidAttribute,
-                          who + " output channels must be divisible by the group count");
+                          who + " " + outName + " channels must be divisible by the group count");
+  return ok();
+}
+inline ErrorObject requireLayout(const TensorPtr &t) {
+  FUSILLI_RETURN_ERROR_IF(!layoutOk(t), ErrorCode::NotImplemented, notChannelsLastMsg(t));
   return ok();
 }
 
@@ -109,11 +137,14 @@ inline ErrorObject checkGroups(const std::string &who, int64_t inC, int64_t outC
 class ConvFPropNode : public INode {
 public:
   ConvFPropAttr convFPropAttr;
-  explicit ConvFPropNode(ConvFPropAttr &&a) : convFPropAttr(std::move(a)) {}
+  ConvFPropNode(ConvFPropAttr &&a, const Context &ctx) : INode(ctx), convFPropAttr(std::move(a)) {}
   const std::string &getName() const override { return convFPropAttr.getName(); }
   Type getType() const override { return Type::Convolution; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = convFPropAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating ConvFPropNode '" << getName() << "'");
+    const auto &a = convFPropAttr;
+    FUSILLI_CHECK_ERROR(detail::checkConvGeometrySet("Conv", a));
     TensorPtr x = a.getX(), w = a.getW(), y = a.getY();
     FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "Conv input tensor X not set");
     FUSILLI_RETURN_ERROR_IF(!w, ErrorCode::AttributeNotSet, "Conv weight tensor W not set");
@@ -122,22 +153,35 @@ public:
                             "Conv input tensor X must have a rank of at least 3");
     FUSILLI_RETURN_ERROR_IF(x->getDim().size() != w->getDim().size(), ErrorCode::InvalidAttribute,
                             "Conv input tensor X and weight tensor W have different ranks");
-    FUSILLI_CHECK_ERROR(detail::checkConvGeometry("Conv", a, x->getDim().size()));
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(x), ErrorCode::NotImplemented, detail::notChannelsLastMsg(x));
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(w), ErrorCode::NotImplemented, detail::notChannelsLastMsg(w));
-    FUSILLI_CHECK_ERROR(detail::checkGroups("Conv", x->getDim()[1], w->getDim()[0], w->getDim()[1]));
-    a.fillFromContext(ctx);
-    const auto inferred = getConvInferredOutputShape(x->getDim(), w->getDim(), a.getDilation(), a.getPadding(),
-                                                     a.getStride());
-    if (y->getDim().empty()) y->setDim(inferred);
+    FUSILLI_CHECK_ERROR(detail::checkConvGeometryRank("Conv", a, x->getDim().size()));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(x));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(w));
+    return detail::checkGroups("Conv", "input", "output", x->getDim()[1], w->getDim()[0], w->getDim()[1]);
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for ConvFPropNode '" << getName() << "'");
+    auto &a = convFPropAttr;
+    a.fillFromContext(context);
+    TensorPtr x = a.getX(), w = a.getW(), y = a.getY();
+    if (y->getDim().empty())
+      y->setDim(getConvInferredOutputShape(x->getDim(), w->getDim(), a.getDilation(), a.getPadding(), a.getStride()));
     if (y->getStride().empty()) y->setStride(detail::strideLike(x, y->getDim()));
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating ConvFPropNode '" << getName() << "'");
+    const auto &a = convFPropAttr;
+    TensorPtr x = a.getX(), w = a.getW(), y = a.getY();
     FUSILLI_RETURN_ERROR_IF(y->getDim().size() < 3, ErrorCode::InvalidAttribute,
                             "Conv output tensor Y must have a rank of at least 3");
-    FUSILLI_RETURN_ERROR_IF(y->getDim() != inferred, ErrorCode::InvalidAttribute,
+    FUSILLI_RETURN_ERROR_IF(x->getDim().size() != y->getDim().size(), ErrorCode::InvalidAttribute,
+                            "Conv input tensor X and output tensor Y have different ranks");
+    FUSILLI_RETURN_ERROR_IF(y->getDim() != getConvInferredOutputShape(x->getDim(), w->getDim(), a.getDilation(),
+                                                                      a.getPadding(), a.getStride()),
+                            ErrorCode::InvalidAttribute,
                             "Conv output tensor Y dimensions do not match the expected shapes inferred "
                             "based on the input and weight dimensions");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(y), ErrorCode::NotImplemented, detail::notChannelsLastMsg(y));
-    return ok();
+    return detail::requireLayout(y);
   }
   void describe(fb_node_desc &d, const TensorId &id) const override {
     detail::initDesc(d, FB_OP_CONV_FPROP);
@@ -151,11 +195,14 @@ public:
 class ConvWGradNode : public INode {
 public:
   ConvWGradAttr convWGradAttr;
-  explicit ConvWGradNode(ConvWGradAttr &&a) : convWGradAttr(std::move(a)) {}
+  ConvWGradNode(ConvWGradAttr &&a, const Context &ctx) : INode(ctx), convWGradAttr(std::move(a)) {}
   const std::string &getName() const override { return convWGradAttr.getName(); }
   Type getType() const override { return Type::WGrad; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = convWGradAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating ConvWGradNode '" << getName() << "'");
+    const auto &a = convWGradAttr;
+    FUSILLI_CHECK_ERROR(detail::checkConvGeometrySet("ConvWGrad", a));
     TensorPtr dy = a.getDY(), x = a.getX(), dw = a.getDW();
     FUSILLI_RETURN_ERROR_IF(!dy, ErrorCode::AttributeNotSet, "ConvWGrad gradient tensor DY not set");
     FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "ConvWGrad input tensor X not set");
@@ -164,21 +211,35 @@ public:
                             "ConvWGrad input tensors DY/X must have a rank of at least 3");
     FUSILLI_RETURN_ERROR_IF(dy->getDim().size() != x->getDim().size(), ErrorCode::InvalidAttribute,
                             "ConvWGrad tensors DY and X have different ranks");
-    FUSILLI_CHECK_ERROR(detail::checkConvGeometry("ConvWGrad", a, x->getDim().size()));
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(dy), ErrorCode::NotImplemented, detail::notChannelsLastMsg(dy));
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(x), ErrorCode::NotImplemented, detail::notChannelsLastMsg(x));
+    FUSILLI_CHECK_ERROR(detail::checkConvGeometryRank("ConvWGrad", a, dy->getDim().size()));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(dy));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(x));
+    // The filter extent cannot be inferred (the group count is unknown), so DW's dims are an input.
+    FUSILLI_RETURN_ERROR_IF(dw->getDim().size() < 2, ErrorCode::InvalidAttribute,
+                            "ConvWGrad weight gradient tensor DW must have a rank of at least 3");
+    return detail::checkGroups("ConvWGrad", "input (X)", "output (DY)", x->getDim()[1], dy->getDim()[1],
+                               dw->getDim()[1]);
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for ConvWGradNode '" << getName() << "'");
+    auto &a = convWGradAttr;
+    a.fillFromContext(context);
+    TensorPtr dy = a.getDY(), dw = a.getDW();
+    if (dw->getStride().empty()) dw->setStride(detail::strideLike(dy, dw->getDim()));
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating ConvWGradNode '" << getName() << "'");
+    const auto &a = convWGradAttr;
+    TensorPtr dy = a.getDY(), x = a.getX(), dw = a.getDW();
     FUSILLI_RETURN_ERROR_IF(dw->getDim().size() < 3, ErrorCode::InvalidAttribute,
                             "ConvWGrad weight gradient tensor DW must have a rank of at least 3");
-    FUSILLI_CHECK_ERROR(detail::checkGroups("ConvWGrad", x->getDim()[1], dy->getDim()[1], dw->getDim()[1]));
-    a.fillFromContext(ctx);
-    if (dw->getStride().empty()) dw->setStride(detail::strideLike(dy, dw->getDim()));
     FUSILLI_RETURN_ERROR_IF(dy->getDim() != getConvInferredOutputShape(x->getDim(), dw->getDim(), a.getDilation(),
                                                                        a.getPadding(), a.getStride()),
                             ErrorCode::InvalidAttribute,
                             "ConvWGrad output DW dimensions do not match the expected shapes inferred based on "
                             "input dimensions");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(dw), ErrorCode::NotImplemented, detail::notChannelsLastMsg(dw));
-    return ok();
+    return detail::requireLayout(dw);
   }
   void describe(fb_node_desc &d, const TensorId &id) const override {
     detail::initDesc(d, FB_OP_CONV_WGRAD);
@@ -192,35 +253,50 @@ public:
 class ConvDGradNode : public INode {
 public:
   ConvDGradAttr convDGradAttr;
-  explicit ConvDGradNode(ConvDGradAttr &&a) : convDGradAttr(std::move(a)) {}
+  ConvDGradNode(ConvDGradAttr &&a, const Context &ctx) : INode(ctx), convDGradAttr(std::move(a)) {}
   const std::string &getName() const override { return convDGradAttr.getName(); }
   Type getType() const override { return Type::DGrad; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = convDGradAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating ConvDGradNode '" << getName() << "'");
+    const auto &a = convDGradAttr;
+    FUSILLI_CHECK_ERROR(detail::checkConvGeometrySet("ConvDGrad", a));
     TensorPtr dy = a.getDY(), w = a.getW(), dx = a.getDX();
     FUSILLI_RETURN_ERROR_IF(!dy, ErrorCode::AttributeNotSet, "ConvDGrad gradient tensor DY not set");
-    FUSILLI_RETURN_ERROR_IF(!w, ErrorCode::AttributeNotSet, "ConvDGrad weight tensor W not set");
+    FUSILLI_RETURN_ERROR_IF(!w, ErrorCode::AttributeNotSet, "ConvDGrad input tensor W not set");
     FUSILLI_RETURN_ERROR_IF(!dx, ErrorCode::AttributeNotSet, "ConvDGrad output tensor DX not set");
-    FUSILLI_RETURN_ERROR_IF(dy->getDim().size() < 3, ErrorCode::InvalidAttribute,
+    FUSILLI_RETURN_ERROR_IF(dy->getDim().size() < 3 || w->getDim().size() < 3, ErrorCode::InvalidAttribute,
                             "ConvDGrad input tensors DY/W must have a rank of at least 3");
-    FUSILLI_RETURN_ERROR_IF(dy->getDim().size() != w->getDim().size(), ErrorCode::InvalidAttribute,
-                            "ConvDGrad tensors DY and W have different ranks");
-    FUSILLI_CHECK_ERROR(detail::checkConvGeometry("ConvDGrad", a, dy->getDim().size()));
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(dy), ErrorCode::NotImplemented, detail::notChannelsLastMsg(dy));
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(w), ErrorCode::NotImplemented, detail::notChannelsLastMsg(w));
+    FUSILLI_CHECK_ERROR(detail::checkConvGeometryRank("ConvDGrad", a, dy->getDim().size()));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(dy));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(w));
+    // DX's extent cannot be inferred (the group count is unknown), so its dims are an input.
+    FUSILLI_RETURN_ERROR_IF(dx->getDim().size() < 2, ErrorCode::InvalidAttribute,
+                            "ConvDGrad input gradient DX must have a rank of at least 3");
+    return detail::checkGroups("ConvDGrad", "input (DX)", "output (DY)", dx->getDim()[1], w->getDim()[0],
+                               w->getDim()[1]);
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for ConvDGradNode '" << getName() << "'");
+    auto &a = convDGradAttr;
+    a.fillFromContext(context);
+    TensorPtr dy = a.getDY(), dx = a.getDX();
+    if (dx->getStride().empty()) dx->setStride(detail::strideLike(dy, dx->getDim()));
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating ConvDGradNode '" << getName() << "'");
+    const auto &a = convDGradAttr;
+    TensorPtr dy = a.getDY(), w = a.getW(), dx = a.getDX();
     FUSILLI_RETURN_ERROR_IF(dx->getDim().size() < 3, ErrorCode::InvalidAttribute,
                             "ConvDGrad input gradient DX must have a rank of at least 3");
-    FUSILLI_CHECK_ERROR(detail::checkGroups("ConvDGrad", dx->getDim()[1], w->getDim()[0], w->getDim()[1]));
-    a.fillFromContext(ctx);
-    if (dx->getStride().empty()) dx->setStride(detail::strideLike(dy, dx->getDim()));
     FUSILLI_RETURN_ERROR_IF(dy->getDim().size() != dx->getDim().size(), ErrorCode::InvalidAttribute,
                             "ConvDGrad tensors DY and DX have different ranks");
     FUSILLI_RETURN_ERROR_IF(dy->getDim() != getConvInferredOutputShape(dx->getDim(), w->getDim(), a.getDilation(),
                                                                        a.getPadding(), a.getStride()),
                             ErrorCode::InvalidAttribute,
                             "ConvDGrad DY dimensions do not match the expected shapes inferred based on DX and W");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(dx), ErrorCode::NotImplemented, detail::notChannelsLastMsg(dx));
-    return ok();
+    return detail::requireLayout(dx);
   }
   void describe(fb_node_desc &d, const TensorId &id) const override {
     detail::initDesc(d, FB_OP_CONV_DGRAD);

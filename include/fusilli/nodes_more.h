@@ -8,11 +8,13 @@ namespace fusilli {
 class MatmulNode : public INode {
 public:
   MatmulAttr matmulAttr;
-  explicit MatmulNode(MatmulAttr &&a) : matmulAttr(std::move(a)) {}
+  MatmulNode(MatmulAttr &&a, const Context &ctx) : INode(ctx), matmulAttr(std::move(a)) {}
   const std::string &getName() const override { return matmulAttr.getName(); }
   Type getType() const override { return Type::Matmul; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &m = matmulAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating MatmulNode '" << getName() << "'");
+    const auto &m = matmulAttr;
     TensorPtr a = m.getA(), b = m.getB(), c = m.getC();
     FUSILLI_RETURN_ERROR_IF(!a, ErrorCode::AttributeNotSet, "Matmul input tensor A not set");
     FUSILLI_RETURN_ERROR_IF(!b, ErrorCode::AttributeNotSet, "Matmul input tensor B not set");
@@ -34,7 +36,7 @@ public:
                                   std::to_string(ad[i]) + ", B has dim=" + std::to_string(bd[i]));
     FUSILLI_CHECK_ERROR(batchDimsOutermost(a, "A"));
     FUSILLI_CHECK_ERROR(batchDimsOutermost(b, "B"));
-    m.fillFromContext(ctx);
+    // Operands of different element types: one batch dim, equal on both sides.
     if (a->getDataType() != b->getDataType()) {
       FUSILLI_RETURN_ERROR_IF(ra != 3, ErrorCode::InvalidAttribute,
                               "Mixed precision matmul is only supported when input tensors A and B are of "
@@ -44,17 +46,29 @@ public:
                               "dimensions (no broadcast): A has batch dim=" + std::to_string(ad[0]) +
                                   ", B has batch dim=" + std::to_string(bd[0]));
     }
-    const auto inferred = getMatmulInferredOutputShape(ad, bd);
-    if (c->getDim().empty()) c->setDim(inferred);
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for MatmulNode '" << getName() << "'");
+    auto &m = matmulAttr;
+    m.fillFromContext(context);
+    TensorPtr a = m.getA(), b = m.getB(), c = m.getC();
+    if (c->getDim().empty()) c->setDim(getMatmulInferredOutputShape(a->getDim(), b->getDim()));
     if (c->getStride().empty())
       c->setStride(generateStrideFromDim(c->getDim(), getContiguousStrideOrder(c->getDim().size())));
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating MatmulNode '" << getName() << "'");
+    const auto &m = matmulAttr;
+    TensorPtr a = m.getA(), b = m.getB(), c = m.getC();
     FUSILLI_RETURN_ERROR_IF(c->getDim().size() < 2, ErrorCode::InvalidAttribute,
                             "Matmul output tensor C must have a rank of at least 2");
-    FUSILLI_RETURN_ERROR_IF(c->getDim() != inferred, ErrorCode::InvalidAttribute,
+    FUSILLI_RETURN_ERROR_IF(c->getDim() != getMatmulInferredOutputShape(a->getDim(), b->getDim()),
+                            ErrorCode::InvalidAttribute,
                             "Matmul output tensor C dimensions do not match the expected shapes inferred "
                             "based on the input dimensions");
-    FUSILLI_CHECK_ERROR(batchDimsOutermost(c, "C"));
-    return ok();
+    return batchDimsOutermost(c, "C");
   }
   void describe(fb_node_desc &d, const TensorId &id) const override {
     detail::initDesc(d, FB_OP_MATMUL);
@@ -77,11 +91,13 @@ private:
 class SdpaNode : public INode {
 public:
   SdpaAttr sdpaAttr;
-  explicit SdpaNode(SdpaAttr &&a) : sdpaAttr(std::move(a)) {}
+  SdpaNode(SdpaAttr &&a, const Context &ctx) : INode(ctx), sdpaAttr(std::move(a)) {}
   const std::string &getName() const override { return sdpaAttr.getName(); }
   Type getType() const override { return Type::Sdpa; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = sdpaAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating SdpaNode '" << getName() << "'");
+    const auto &a = sdpaAttr;
     TensorPtr q = a.getQ(), k = a.getK(), v = a.getV(), o = a.getO(), mask = a.getMASK();
     FUSILLI_RETURN_ERROR_IF(!q, ErrorCode::AttributeNotSet, "SDPA input tensor Q not set");
     FUSILLI_RETURN_ERROR_IF(!k, ErrorCode::AttributeNotSet, "SDPA input tensor K not set");
@@ -123,17 +139,32 @@ public:
       FUSILLI_RETURN_ERROR_IF(md.size() != 4, ErrorCode::InvalidAttribute, "SDPA attention mask must be rank 4");
       const int64_t full[4] = {qd[0], hq, qd[2], kd[2]};
       const char *what[4] = {"batch dim", "heads dim", "seq_q dim", "seq_kv dim"};
+      const char *match[4] = {"input batch", "Q heads", "Q sequence length", "KV sequence length"};
       for (int i = 0; i < 4; ++i)
         FUSILLI_RETURN_ERROR_IF(md[i] != 1 && md[i] != full[i], ErrorCode::InvalidAttribute,
                                 std::string("SDPA attention mask ") + what[i] + " (" + std::to_string(md[i]) +
-                                    ") must be 1 or match (" + std::to_string(full[i]) + ")");
+                                    ") must be 1 or match " + match[i] + " (" + std::to_string(full[i]) + ")");
     }
     FUSILLI_RETURN_ERROR_IF(a.getDropout() < 0.f || a.getDropout() >= 1.f, ErrorCode::InvalidAttribute,
                             "SDPA dropout probability must be in [0, 1)");
-    a.fillFromContext(ctx);
-    const std::vector<int64_t> od = {qd[0], qd[1], qd[2], vd[3]};
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for SdpaNode '" << getName() << "'");
+    auto &a = sdpaAttr;
+    a.fillFromContext(context);
+    TensorPtr q = a.getQ(), v = a.getV(), o = a.getO();
+    const std::vector<int64_t> od = {q->getDim()[0], q->getDim()[1], q->getDim()[2], v->getDim()[3]};
     if (o->getDim().empty()) o->setDim(od);
-    if (o->getStride().empty()) o->setStride(generateStrideFromDim(od, getContiguousStrideOrder(4)));
+    if (o->getStride().empty())
+      o->setStride(generateStrideFromDim(o->getDim(), getContiguousStrideOrder(o->getDim().size())));
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating SdpaNode '" << getName() << "'");
+    const auto &a = sdpaAttr;
+    TensorPtr q = a.getQ(), v = a.getV(), o = a.getO();
+    const std::vector<int64_t> od = {q->getDim()[0], q->getDim()[1], q->getDim()[2], v->getDim()[3]};
     FUSILLI_RETURN_ERROR_IF(o->getDim() != od, ErrorCode::InvalidAttribute,
                             "SDPA output tensor O dimensions do not match expected shape "
                             "[batch, headsQ, seqQ, headDim]");
@@ -156,29 +187,42 @@ public:
   }
 };
 
-namespace detail {
-// scale / bias of a norm: X's shape with the batch dim set to 1, X's memory order
-// (reference norm_utils.h:53-99).
-inline void inferScaleBias(const TensorPtr &t, const TensorPtr &x) {
-  if (t->getDim().empty()) {
-    auto d = x->getDim();
-    d[0] = 1;
-    t->setDim(d);
-  }
-  if (t->getStride().empty())
-    t->setStride(generateStrideFromDim(t->getDim(),
-                                       generateStrideOrderPreservingFormat(x->getStride(), t->getDim().size())));
+// Shape helpers shared by the norms (reference node/norm_utils.h:40-99).
+namespace norm_utils {
+// [B, 1, ..., 1] and its contiguous strides: the shape of MEAN / INV_VARIANCE / INV_RMS.
+inline std::pair<std::vector<int64_t>, std::vector<int64_t>>
+getTrainingForwardOutputDimAndStride(const std::vector<int64_t> &xDim, size_t batchDim = 0) {
+  std::vector<int64_t> dim(xDim.size(), 1);
+  dim[batchDim] = xDim[batchDim];
+  return {dim, generateStrideFromDim(dim, getContiguousStrideOrder(dim.size()))};
 }
+// X's shape with the batch dim set to 1: the shape of SCALE / BIAS.
+inline std::vector<int64_t> getScaleBiasDim(const std::vector<int64_t> &xDim, size_t batchDim = 0) {
+  auto dim = xDim;
+  dim[batchDim] = 1;
+  return dim;
+}
+inline std::vector<int64_t> getScaleBiasStride(const std::vector<int64_t> &dim, const std::vector<int64_t> &xStride) {
+  return generateStrideFromDim(dim, generateStrideOrderPreservingFormat(xStride, dim.size()));
+}
+inline void inferDimAndStride(const TensorPtr &t, const std::vector<int64_t> &dim, const std::vector<int64_t> &stride) {
+  if (t->getDim().empty()) t->setDim(dim);
+  if (t->getStride().empty()) t->setStride(stride);
+}
+inline void inferScaleBiasDimAndStride(const TensorPtr &t, const std::vector<int64_t> &xDim,
+                                       const std::vector<int64_t> &xStride) {
+  if (t->getDim().empty()) t->setDim(getScaleBiasDim(xDim));
+  if (t->getStride().empty()) t->setStride(getScaleBiasStride(t->getDim(), xStride));
+}
+} // namespace norm_utils
+
+namespace detail {
 inline ErrorObject checkScaleBias(const std::string &who, const char *which, const TensorPtr &t, const TensorPtr &x) {
   if (!t) return ok();
-  if (!t->getDim().empty()) {
-    auto d = x->getDim();
-    d[0] = 1;
-    FUSILLI_RETURN_ERROR_IF(t->getDim() != d, ErrorCode::InvalidAttribute,
+  if (!t->getDim().empty())
+    FUSILLI_RETURN_ERROR_IF(t->getDim() != norm_utils::getScaleBiasDim(x->getDim()), ErrorCode::InvalidAttribute,
                             who + " input tensor " + which + " must have shape as tensor X with single batch");
-  }
-  if (!t->getStride().empty())
-    FUSILLI_RETURN_ERROR_IF(!layoutOk(t), ErrorCode::NotImplemented, notChannelsLastMsg(t));
+  if (!t->getStride().empty()) FUSILLI_CHECK_ERROR(requireLayout(t));
   return ok();
 }
 } // namespace detail
@@ -186,12 +230,14 @@ inline ErrorObject checkScaleBias(const std::string &who, const char *which, con
 class LayerNormNode : public INode {
 public:
   LayernormAttr layernormAttr;
-  explicit LayerNormNode(LayernormAttr &&a) : layernormAttr(std::move(a)) {}
+  LayerNormNode(LayernormAttr &&a, const Context &ctx) : INode(ctx), layernormAttr(std::move(a)) {}
   const std::string &getName() const override { return layernormAttr.getName(); }
   Type getType() const override { return Type::LayerNorm; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = layernormAttr;
-    const bool training = a.getForwardPhase() == NormFwdPhase::TRAINING;
+  bool isTrainingForwardPhase() const { return layernormAttr.getForwardPhase() == NormFwdPhase::TRAINING; }
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating LayerNormNode '" << getName() << "'");
+    const auto &a = layernormAttr;
     FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::NOT_SET, ErrorCode::AttributeNotSet,
                             "LayerNorm forward phase not set");
     TensorPtr x = a.getX(), s = a.getSCALE(), b = a.getBIAS(), y = a.getY(), m = a.getMEAN(),
@@ -200,10 +246,10 @@ public:
     FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "LayerNorm output tensor Y not set");
     FUSILLI_RETURN_ERROR_IF(x->getDim().size() < 2, ErrorCode::InvalidAttribute,
                             "LayerNorm input tensor X must have a rank of at least 2");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(x), ErrorCode::NotImplemented, detail::notChannelsLastMsg(x));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(x));
     FUSILLI_CHECK_ERROR(detail::checkScaleBias("LayerNorm", "SCALE", s, x));
     FUSILLI_CHECK_ERROR(detail::checkScaleBias("LayerNorm", "BIAS", b, x));
-    if (training) {
+    if (isTrainingForwardPhase()) {
       FUSILLI_RETURN_ERROR_IF(!m, ErrorCode::AttributeNotSet, "LayerNorm output tensor MEAN not set");
       FUSILLI_RETURN_ERROR_IF(!v, ErrorCode::AttributeNotSet, "LayerNorm output tensor INV_VARIANCE not set");
     } else {
@@ -213,31 +259,42 @@ public:
     }
     FUSILLI_RETURN_ERROR_IF(!e, ErrorCode::AttributeNotSet, "LayerNorm epsilon not set");
     FUSILLI_RETURN_ERROR_IF(!e->isScalar(), ErrorCode::InvalidAttribute, "LayerNorm epsilon must be a scalar constant");
-    a.fillFromContext(ctx);
-    if (s) detail::inferScaleBias(s, x);
-    if (b) detail::inferScaleBias(b, x);
-    if (y->getDim().empty()) y->setDim(x->getDim());
-    if (y->getStride().empty()) y->setStride(x->getStride());
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for LayerNormNode '" << getName() << "'");
+    auto &a = layernormAttr;
+    a.fillFromContext(context);
+    TensorPtr x = a.getX(), s = a.getSCALE(), b = a.getBIAS(), y = a.getY();
+    if (s) norm_utils::inferScaleBiasDimAndStride(s, x->getDim(), x->getStride());
+    if (b) norm_utils::inferScaleBiasDimAndStride(b, x->getDim(), x->getStride());
+    norm_utils::inferDimAndStride(y, x->getDim(), x->getStride());
+    if (isTrainingForwardPhase()) {
+      const auto [dim, stride] = norm_utils::getTrainingForwardOutputDimAndStride(x->getDim());
+      norm_utils::inferDimAndStride(a.getMEAN(), dim, stride);
+      norm_utils::inferDimAndStride(a.getINV_VARIANCE(), dim, stride);
+    }
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating LayerNormNode '" << getName() << "'");
+    const auto &a = layernormAttr;
+    TensorPtr x = a.getX(), y = a.getY();
     FUSILLI_RETURN_ERROR_IF(x->getDim() != y->getDim(), ErrorCode::InvalidAttribute,
                             "LayerNorm output Y tensor must have the same shape as input X tensor");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(y), ErrorCode::NotImplemented, detail::notChannelsLastMsg(y));
-    if (training) {
-      std::vector<int64_t> sd(x->getDim().size(), 1);
-      sd[0] = x->getDim()[0];
-      const auto ss = generateStrideFromDim(sd, getContiguousStrideOrder(sd.size()));
-      for (const TensorPtr &t : {m, v}) {
-        if (t->getDim().empty()) t->setDim(sd);
-        if (t->getStride().empty()) t->setStride(ss);
-      }
-      FUSILLI_RETURN_ERROR_IF(m->getDim() != sd, ErrorCode::InvalidAttribute,
+    FUSILLI_CHECK_ERROR(detail::requireLayout(y));
+    if (isTrainingForwardPhase()) {
+      const auto [dim, stride] = norm_utils::getTrainingForwardOutputDimAndStride(x->getDim());
+      TensorPtr m = a.getMEAN(), v = a.getINV_VARIANCE();
+      FUSILLI_RETURN_ERROR_IF(m->getDim() != dim, ErrorCode::InvalidAttribute,
                               "Layernorm output MEAN tensor must have shape [B, 1, ..., 1] with rank equal to "
                               "input X tensor's rank, and batch dimension equal to input X tensor's batch dimension");
-      FUSILLI_RETURN_ERROR_IF(v->getDim() != sd, ErrorCode::InvalidAttribute,
+      FUSILLI_RETURN_ERROR_IF(v->getDim() != dim, ErrorCode::InvalidAttribute,
                               "LayerNorm output INV_VARIANCE tensor must have shape [B, 1, ..., 1] with  rank equal "
                               "to input X tensor's rank, and batch dimension equal to input X tensor's batch dimension");
-      FUSILLI_RETURN_ERROR_IF(m->getStride() != ss, ErrorCode::InvalidAttribute,
+      FUSILLI_RETURN_ERROR_IF(m->getStride() != stride, ErrorCode::InvalidAttribute,
                               "LayerNorm output MEAN tensor must have unit strides");
-      FUSILLI_RETURN_ERROR_IF(v->getStride() != ss, ErrorCode::InvalidAttribute,
+      FUSILLI_RETURN_ERROR_IF(v->getStride() != stride, ErrorCode::InvalidAttribute,
                               "LayerNorm output INV_VARIANCE tensor must have unit strides");
     }
     return ok();
@@ -251,38 +308,71 @@ public:
     d.outputs[0] = id(layernormAttr.getY());
     d.outputs[1] = id(layernormAttr.getMEAN());
     d.outputs[2] = id(layernormAttr.getINV_VARIANCE());
-    if (layernormAttr.getForwardPhase() == NormFwdPhase::TRAINING) d.flags |= FB_FLAG_NORM_TRAINING;
+    if (isTrainingForwardPhase()) d.flags |= FB_FLAG_NORM_TRAINING;
   }
 };
 
 class RmsNormNode : public INode {
 public:
   RmsnormAttr rmsnormAttr;
-  explicit RmsNormNode(RmsnormAttr &&a) : rmsnormAttr(std::move(a)) {}
+  RmsNormNode(RmsnormAttr &&a, const Context &ctx) : INode(ctx), rmsnormAttr(std::move(a)) {}
   const std::string &getName() const override { return rmsnormAttr.getName(); }
   Type getType() const override { return Type::RmsNorm; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = rmsnormAttr;
+  bool isTrainingForwardPhase() const { return rmsnormAttr.getForwardPhase() == NormFwdPhase::TRAINING; }
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating RmsNormNode '" << getName() << "'");
+    const auto &a = rmsnormAttr;
     FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::NOT_SET, ErrorCode::AttributeNotSet,
                             "RmsNorm forward phase not set");
-    TensorPtr x = a.getX(), s = a.getSCALE(), y = a.getY(), e = a.getEpsilon();
+    TensorPtr x = a.getX(), s = a.getSCALE(), y = a.getY(), r = a.getINV_RMS(), e = a.getEpsilon();
     FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "RmsNorm input tensor X not set");
     FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "RmsNorm output tensor Y not set");
     FUSILLI_RETURN_ERROR_IF(x->getDim().size() < 2, ErrorCode::InvalidAttribute,
                             "RmsNorm input tensor X must have a rank of at least 2");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(x), ErrorCode::NotImplemented, detail::notChannelsLastMsg(x));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(x));
     FUSILLI_CHECK_ERROR(detail::checkScaleBias("RmsNorm", "SCALE", s, x));
+    if (isTrainingForwardPhase())
+      FUSILLI_RETURN_ERROR_IF(!r, ErrorCode::AttributeNotSet, "RmsNorm output tensor INV_RMS not set");
+    else
+      FUSILLI_RETURN_ERROR_IF(r != nullptr, ErrorCode::InvalidAttribute, "RmsNorm output tensor INV_RMS should not be set");
     FUSILLI_RETURN_ERROR_IF(!e, ErrorCode::AttributeNotSet, "RmsNorm epsilon not set");
     FUSILLI_RETURN_ERROR_IF(!e->isScalar(), ErrorCode::InvalidAttribute, "RmsNorm epsilon must be a scalar constant");
-    FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::TRAINING, ErrorCode::NotImplemented,
-                            "RmsNorm training forward phase is not implemented");
-    a.fillFromContext(ctx);
-    if (s) detail::inferScaleBias(s, x);
-    if (y->getDim().empty()) y->setDim(x->getDim());
-    if (y->getStride().empty()) y->setStride(x->getStride());
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for RmsNormNode '" << getName() << "'");
+    auto &a = rmsnormAttr;
+    a.fillFromContext(context);
+    TensorPtr x = a.getX(), s = a.getSCALE(), y = a.getY();
+    if (s) norm_utils::inferScaleBiasDimAndStride(s, x->getDim(), x->getStride());
+    norm_utils::inferDimAndStride(y, x->getDim(), x->getStride());
+    if (isTrainingForwardPhase()) {
+      const auto [dim, stride] = norm_utils::getTrainingForwardOutputDimAndStride(x->getDim());
+      norm_utils::inferDimAndStride(a.getINV_RMS(), dim, stride);
+    }
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating RmsNormNode '" << getName() << "'");
+    const auto &a = rmsnormAttr;
+    TensorPtr x = a.getX(), y = a.getY();
     FUSILLI_RETURN_ERROR_IF(x->getDim() != y->getDim(), ErrorCode::InvalidAttribute,
                             "RmsNorm output Y tensor must have the same shape as input X tensor");
-    FUSILLI_RETURN_ERROR_IF(!detail::layoutOk(y), ErrorCode::NotImplemented, detail::notChannelsLastMsg(y));
+    FUSILLI_CHECK_ERROR(detail::requireLayout(y));
+    if (isTrainingForwardPhase()) {
+      const auto [dim, stride] = norm_utils::getTrainingForwardOutputDimAndStride(x->getDim());
+      TensorPtr r = a.getINV_RMS();
+      FUSILLI_RETURN_ERROR_IF(r->getDim() != dim, ErrorCode::InvalidAttribute,
+                              "RmsNorm output INV_RMS tensor must have shape [B, 1, ..., 1] with rank equal to "
+                              "input X tensor's rank, and batch dimension equal to input X tensor's batch dimension");
+      FUSILLI_RETURN_ERROR_IF(r->getStride() != stride, ErrorCode::InvalidAttribute,
+                              "RmsNorm output INV_RMS tensor must have unit strides");
+    }
+    // As in the reference (rmsnorm_node.h:203-206) the training variant is declared but refused.
+    FUSILLI_RETURN_ERROR_IF(isTrainingForwardPhase(), ErrorCode::NotImplemented,
+                            "RmsNorm training mode is not yet supported: torch-mlir does not lower the "
+                            "training variant");
     return ok();
   }
   void describe(fb_node_desc &d, const TensorId &id) const override {
@@ -297,7 +387,7 @@ public:
 class ReductionNode : public INode {
 public:
   ReductionAttr reductionAttr;
-  explicit ReductionNode(ReductionAttr &&a) : reductionAttr(std::move(a)) {}
+  ReductionNode(ReductionAttr &&a, const Context &ctx) : INode(ctx), reductionAttr(std::move(a)) {}
   const std::string &getName() const override { return reductionAttr.getName(); }
   Type getType() const override { return Type::Reduction; }
   // dims i with Y[i] == 1 and X[i] > 1
@@ -308,18 +398,32 @@ public:
       if (yd[i] == 1 && xd[i] > 1) dims.push_back(static_cast<int64_t>(i));
     return dims;
   }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = reductionAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating ReductionNode '" << getName() << "'");
+    const auto &a = reductionAttr;
     FUSILLI_RETURN_ERROR_IF(a.getMode() == ReductionAttr::Mode::NOT_SET, ErrorCode::AttributeNotSet,
                             "Reduction mode not set");
+    FUSILLI_RETURN_ERROR_IF(!a.getX(), ErrorCode::AttributeNotSet, "Reduction operation requires X input");
+    FUSILLI_RETURN_ERROR_IF(!a.getY(), ErrorCode::AttributeNotSet, "Reduction operation requires Y output");
+    FUSILLI_RETURN_ERROR_IF(a.getX()->getDim().empty(), ErrorCode::AttributeNotSet,
+                            "Reduction input X dimensions not set");
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for ReductionNode '" << getName() << "'");
+    auto &a = reductionAttr;
+    a.fillFromContext(context);
     TensorPtr x = a.getX(), y = a.getY();
-    FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "Reduction operation requires X input");
-    FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "Reduction operation requires Y output");
-    FUSILLI_RETURN_ERROR_IF(x->getDim().empty(), ErrorCode::AttributeNotSet, "Reduction input X dimensions not set");
-    a.fillFromContext(ctx);
     if (y->getDim().empty()) y->setDim(x->getDim());
     if (y->getStride().empty())
       y->setStride(generateStrideFromDim(y->getDim(), getContiguousStrideOrder(y->getDim().size())));
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating ReductionNode '" << getName() << "'");
+    const auto &a = reductionAttr;
+    TensorPtr x = a.getX(), y = a.getY();
     FUSILLI_RETURN_ERROR_IF(x->getDim().size() != y->getDim().size(), ErrorCode::InvalidAttribute,
                             "Reduction input and output must have the same rank");
     FUSILLI_RETURN_ERROR_IF(a.getMode() == ReductionAttr::Mode::AVG &&
@@ -345,17 +449,19 @@ public:
 class PointwiseNode : public INode {
 public:
   PointwiseAttr pointwiseAttr;
-  explicit PointwiseNode(PointwiseAttr &&a) : pointwiseAttr(std::move(a)) {}
+  PointwiseNode(PointwiseAttr &&a, const Context &ctx) : INode(ctx), pointwiseAttr(std::move(a)) {}
   const std::string &getName() const override { return pointwiseAttr.getName(); }
   Type getType() const override { return Type::Pointwise; }
-  ErrorObject validateNode(const Context &ctx) override {
-    auto &a = pointwiseAttr;
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating PointwiseNode '" << getName() << "'");
+    const auto &a = pointwiseAttr;
     const auto mode = a.getMode();
     FUSILLI_RETURN_ERROR_IF(mode == PointwiseAttr::Mode::NOT_SET, ErrorCode::AttributeNotSet, "Pointwise mode not set");
     const TensorPtr ins[3] = {a.getIN_0(), a.getIN_1(), a.getIN_2()};
     const int need = PointwiseAttr::requiredInputCount(mode);
+    const std::string nm = PointwiseAttr::modeName(mode);
     for (int i = 0; i < 3; ++i) {
-      const std::string nm = std::string(PointwiseAttr::modeName(mode));
       if (i < need)
         FUSILLI_RETURN_ERROR_IF(!ins[i], ErrorCode::AttributeNotSet,
                                 nm + " mode requires IN_" + std::to_string(i) + " input");
@@ -363,10 +469,16 @@ public:
         FUSILLI_RETURN_ERROR_IF(ins[i] != nullptr, ErrorCode::InvalidAttribute,
                                 nm + " mode should not have IN_" + std::to_string(i) + " input set");
     }
+    FUSILLI_RETURN_ERROR_IF(!a.getOUT_0(), ErrorCode::AttributeNotSet, "Pointwise operation requires output");
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for PointwiseNode '" << getName() << "'");
+    auto &a = pointwiseAttr;
     TensorPtr out = a.getOUT_0();
-    FUSILLI_RETURN_ERROR_IF(!out, ErrorCode::AttributeNotSet, "Pointwise operation requires output");
-    if (PointwiseAttr::forcesBooleanOutput(mode)) out->setDataType(DataType::Boolean);
-    a.fillFromContext(ctx);
+    if (PointwiseAttr::forcesBooleanOutput(a.getMode())) out->setDataType(DataType::Boolean);
+    a.fillFromContext(context);
+    const TensorPtr ins[3] = {a.getIN_0(), a.getIN_1(), a.getIN_2()};
     if (out->getDim().empty()) {
       std::vector<std::vector<int64_t>> shapes;
       for (const auto &t : ins)
@@ -375,6 +487,8 @@ public:
       out->setDim(shape);
     }
     if (out->getStride().empty()) {
+      // the first input of the output's shape lends its strides; a virtual output otherwise keeps
+      // IN_0's memory format
       for (const auto &t : ins)
         if (t && t->getDim() == out->getDim()) {
           out->setStride(t->getStride());

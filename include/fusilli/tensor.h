@@ -10,6 +10,8 @@
 #include <memory>
 #include <numeric>
 #include <optional>
+#include <ranges>
+#include <span>
 #include <string>
 #include <utility>
 #include <variant>
@@ -92,6 +94,36 @@ inline ErrorOr<std::vector<int64_t>> generateStrideFromLayout(const std::vector<
   return error(ErrorCode::InvalidArgument, "Invalid layout string: " + layout);
 }
 
+// Permutations between the two supported memory formats, as dimension orders
+// (reference attributes/tensor_attributes.h:274-311).
+inline std::vector<int64_t> getPreserveContiguousPermuteOrder(size_t numDims) {
+  std::vector<int64_t> p(numDims);
+  std::iota(p.begin(), p.end(), 0);
+  return p;
+}
+inline std::vector<int64_t> getChannelsLastToContiguousPermuteOrder(size_t numDims) {
+  // N, then the spatial dims, then C
+  std::vector<int64_t> p(numDims);
+  p[0] = 0;
+  for (size_t i = 2; i < numDims; ++i) p[i] = static_cast<int64_t>(i - 1);
+  p[1] = static_cast<int64_t>(numDims - 1);
+  return p;
+}
+inline std::vector<int64_t> getContiguousToChannelsLastPermuteOrder(size_t numDims) {
+  // N, then C moved to the end of the spatial dims
+  std::vector<int64_t> p(numDims);
+  p[0] = 0;
+  p[numDims - 1] = 1;
+  for (size_t i = 1; i + 1 < numDims; ++i) p[i] = static_cast<int64_t>(i + 1);
+  return p;
+}
+
+// Any range of integers convertible to int64_t that is not already a std::vector<int64_t>.
+template <typename R>
+concept Int64Range = std::ranges::input_range<R> &&
+                     std::convertible_to<std::ranges::range_value_t<R>, int64_t> &&
+                     !std::same_as<std::remove_cvref_t<R>, std::vector<int64_t>>;
+
 inline std::vector<int64_t> inversePermutation(const std::vector<int64_t> &perm) {
   std::vector<int64_t> inv(perm.size());
   for (size_t i = 0; i < perm.size(); ++i) inv[perm[i]] = static_cast<int64_t>(i);
@@ -131,6 +163,24 @@ public:
   TensorAttr &setDataType(DataType t) { dtype_ = t; return *this; }
   TensorAttr &setDim(const std::vector<int64_t> &d) { dim_ = d; return *this; }
   TensorAttr &setStride(const std::vector<int64_t> &s) { stride_ = s; return *this; }
+  template <Int64Range R> TensorAttr &setDim(R &&d) { dim_.assign(d.begin(), d.end()); return *this; }
+  template <Int64Range R> TensorAttr &setStride(R &&s) { stride_.assign(s.begin(), s.end()); return *this; }
+  // Dynamic dims are part of the reference's tensor description (tensor_attributes.h:512-570);
+  // the B200 backend builds plans for static shapes only and refuses graphs that use them.
+  TensorAttr &setDynamicDim(size_t index) {
+    dynamic_.push_back(index);
+    canonicalizeDynamicDims();
+    return *this;
+  }
+  TensorAttr &setDynamicDims(std::span<const size_t> indices) {
+    dynamic_.assign(indices.begin(), indices.end());
+    canonicalizeDynamicDims();
+    return *this;
+  }
+  TensorAttr &setDynamicDims(std::initializer_list<size_t> indices) {
+    return setDynamicDims(std::span<const size_t>(indices.begin(), indices.size()));
+  }
+  TensorAttr &clearDynamicDims() { dynamic_.clear(); return *this; }
   TensorAttr &setIsVirtual(bool v) { virtual_ = v; return *this; }
   TensorAttr &setOutput(bool isOutput) { return setIsVirtual(!isOutput); }
   TensorAttr &setIsScalar(bool v) { scalar_ = v; return *this; }
@@ -142,6 +192,9 @@ public:
   const std::vector<int64_t> &getStride() const { return stride_; }
   bool isVirtual() const { return virtual_; }
   bool isScalar() const { return scalar_; }
+  bool isDynamicDim(size_t index) const { return std::binary_search(dynamic_.begin(), dynamic_.end(), index); }
+  bool hasDynamicDims() const { return !dynamic_.empty(); }
+  const std::vector<size_t> &getDynamicDims() const { return dynamic_; }
   std::optional<scalar_t> getScalarValue() const { return value_; }
   double scalarAsDouble() const {
     return value_ ? std::visit([](auto v) { return static_cast<double>(v); }, *value_) : 0.0;
@@ -227,6 +280,20 @@ public:
     FUSILLI_RETURN_ERROR_IF(stride_.empty(), ErrorCode::AttributeNotSet, who + " strides not set");
     FUSILLI_RETURN_ERROR_IF(dim_.size() != stride_.size(), ErrorCode::InvalidAttribute,
                             who + " uses dim and stride of different dimensionality");
+    for (size_t d : dynamic_) {
+      FUSILLI_RETURN_ERROR_IF(d >= dim_.size(), ErrorCode::InvalidAttribute,
+                              who + " has dynamic dim index " + std::to_string(d) + " out of range for rank " +
+                                  std::to_string(dim_.size()));
+      FUSILLI_RETURN_ERROR_IF(stride_[d] == 0, ErrorCode::InvalidAttribute,
+                              who + " has dynamic dim at index " + std::to_string(d) +
+                                  " with stride 0 (broadcast stride), which is not supported");
+      FUSILLI_RETURN_ERROR_IF(dim_[d] == 1, ErrorCode::InvalidAttribute,
+                              who + " has dynamic dim at index " + std::to_string(d) +
+                                  " with representative size 1, which is not supported");
+    }
+    FUSILLI_RETURN_ERROR_IF(hasBroadcastDims() && hasDynamicDims(), ErrorCode::InvalidAttribute,
+                            who + " has dynamic dimensions on a tensor with broadcast strides, which is not "
+                                  "supported");
     FUSILLI_RETURN_ERROR_IF(!hasValidPhysicalRepresentation(), ErrorCode::InvalidAttribute,
                             who + " has invalid physical representation. It must be a valid "
                                   "permutation of the logical dimensions");
@@ -250,6 +317,11 @@ private:
   std::string name_;
   DataType dtype_ = DataType::NotSet;
   std::vector<int64_t> dim_, stride_;
+  std::vector<size_t> dynamic_;
+  void canonicalizeDynamicDims() {
+    std::sort(dynamic_.begin(), dynamic_.end());
+    dynamic_.erase(std::unique(dynamic_.begin(), dynamic_.end()), dynamic_.end());
+  }
   bool virtual_ = false, scalar_ = false;
   std::optional<scalar_t> value_;
 };

@@ -10,10 +10,28 @@
 #include <catch2/catch_test_macros.hpp>
 
 #include <cstdint>
+#include <functional>
 #include <memory>
 #include <optional>
 #include <span>
 #include <vector>
+
+// Runs a clean-up callback when the scope ends, also when a REQUIRE aborts the test case.
+class [[nodiscard]] ScopeExit {
+public:
+  explicit ScopeExit(std::function<void()> &&f) : fn_(std::move(f)) {}
+  ScopeExit(ScopeExit &&o) noexcept : fn_(std::move(o.fn_)) { o.release(); }
+  ScopeExit(const ScopeExit &) = delete;
+  ScopeExit &operator=(const ScopeExit &) = delete;
+  ScopeExit &operator=(ScopeExit &&) = delete;
+  void release() { fn_ = nullptr; }
+  ~ScopeExit() {
+    if (fn_) fn_();
+  }
+
+private:
+  std::function<void()> fn_;
+};
 
 #define FUSILLI_REQUIRE_OK(expr)                                                                     \
   do {                                                                                               \
@@ -72,6 +90,10 @@ inline TensorAttr createTestTensorAttr(const std::string &name, std::span<const 
   TensorAttr t;
   t.setName(name).setDim(d).setStride(generateStrideFromDim(d, getContiguousStrideOrder(d.size())));
   return t;
+}
+
+inline std::shared_ptr<TensorAttr> createTestTensor(const std::string &name, std::span<const int64_t> dim, Graph *graph) {
+  return graph->tensor(createTestTensorAttr(name, dim));
 }
 
 } // namespace fusilli

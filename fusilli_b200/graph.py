@@ -560,15 +560,16 @@ def _v_conv_common(nm, attr, rank):
              f"{nm} dilation size does not match number of spatial dimensions")
 
 
-def _v_groups(nm, inC, outC, fC):
+def _v_groups(nm, inC, outC, fC, in_name="input", out_name="output"):
+    filt = "filter" if in_name == "input" else "filter (W)"
     _require(inC % fC == 0, ErrorCode.InvalidAttribute,
-             f"{nm} input channels must be divisible by the filter channels")
+             f"{nm} {in_name} channels must be divisible by the {filt} channels")
     g = inC // fC
     _require(0 < g <= inC and g <= outC, ErrorCode.InvalidAttribute,
              f"{nm} group count must be greater than 0 and less than or equal to the "
              "numbers of input and outputs channels")
     _require(outC % g == 0, ErrorCode.InvalidAttribute,
-             f"{nm} output channels must be divisible by the group count")
+             f"{nm} {out_name} channels must be divisible by the group count")
 
 
 def _v_conv_fprop(g: GraphBase, n: Node):
@@ -612,7 +613,7 @@ def _v_conv_wgrad(g: GraphBase, n: Node):
     _require(_layout_ok(x), ErrorCode.NotImplemented, _not_cl(x))
     _require(len(dw.dim) >= 3, ErrorCode.InvalidAttribute,
              "ConvWGrad weight gradient tensor DW must have a rank of at least 3")
-    _v_groups("ConvWGrad", x.dim[1], dy.dim[1], dw.dim[1])
+    _v_groups("ConvWGrad", x.dim[1], dy.dim[1], dw.dim[1], "input (X)", "output (DY)")
     g._fill(n)
     if not dw.stride:
         dw.setStride(contiguousStride(dw.dim) if dy.isContiguous() else channelsLastStride(dw.dim))
@@ -628,7 +629,7 @@ def _v_conv_dgrad(g: GraphBase, n: Node):
     dx = n.outputs[0]
     a = n.attr
     _require(dy is not None, ErrorCode.AttributeNotSet, "ConvDGrad gradient tensor DY not set")
-    _require(w is not None, ErrorCode.AttributeNotSet, "ConvDGrad weight tensor W not set")
+    _require(w is not None, ErrorCode.AttributeNotSet, "ConvDGrad input tensor W not set")
     _require(len(dy.dim) >= 3, ErrorCode.InvalidAttribute,
              "ConvDGrad input tensors DY/W must have a rank of at least 3")
     _require(len(dy.dim) == len(w.dim), ErrorCode.InvalidAttribute,
@@ -638,7 +639,7 @@ def _v_conv_dgrad(g: GraphBase, n: Node):
     _require(_layout_ok(w), ErrorCode.NotImplemented, _not_cl(w))
     _require(len(dx.dim) >= 3, ErrorCode.InvalidAttribute,
              "ConvDGrad input gradient DX must have a rank of at least 3")
-    _v_groups("ConvDGrad", dx.dim[1], w.dim[0], w.dim[1])
+    _v_groups("ConvDGrad", dx.dim[1], w.dim[0], w.dim[1], "input (DX)", "output (DY)")
     g._fill(n)
     if not dx.stride:
         dx.setStride(contiguousStride(dx.dim) if dy.isContiguous() else channelsLastStride(dx.dim))
@@ -727,9 +728,10 @@ def _v_sdpa(g: GraphBase, n: Node):
         _require(len(mask.dim) == 4, ErrorCode.InvalidAttribute, "SDPA attention mask must be rank 4")
         full = [q.dim[0], hq, q.dim[2], k.dim[2]]
         what = ["batch dim", "heads dim", "seq_q dim", "seq_kv dim"]
+        match = ["input batch", "Q heads", "Q sequence length", "KV sequence length"]
         for i in range(4):
             _require(mask.dim[i] in (1, full[i]), ErrorCode.InvalidAttribute,
-                     f"SDPA attention mask {what[i]} ({mask.dim[i]}) must be 1 or match ({full[i]})")
+                     f"SDPA attention mask {what[i]} ({mask.dim[i]}) must be 1 or match {match[i]} ({full[i]})")
     _require(0.0 <= a.dropout < 1.0, ErrorCode.InvalidAttribute,
              "SDPA dropout probability must be in [0, 1)")
     g._fill(n)
@@ -774,7 +776,8 @@ def _v_norm(g: GraphBase, n: Node, nm: str):
     _require(eps.isScalar(), ErrorCode.InvalidAttribute, f"{nm} epsilon must be a scalar constant")
     if n.op == Op.RMSNORM:
         _require(a.forwardPhase != NormFwdPhase.TRAINING, ErrorCode.NotImplemented,
-                 "RmsNorm training forward phase is not implemented")
+                 "RmsNorm training mode is not yet supported: torch-mlir does not lower the "
+                 "training variant")
     g._fill(n)
     for t in affine:
         if t is not None:

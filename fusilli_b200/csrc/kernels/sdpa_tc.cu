@@ -1,23 +1,24 @@
 // Flash-style scaled-dot-product attention forward on the tensor cores:
 //   O = softmax(Q K^T * scale [causal]) V,  Q/K/V/O contiguous [B,H,S,128], bf16 or f16.
 //
-// One CTA per (128-query block, batch*head). Memory stays O(S): K/V stream through a
-// 2-stage shared-memory ring and the 128x128 score tile never leaves the SM.
-//   warp 0      TMA producer: Q once, then K_j / V_j tiles (128 keys x 128 dims, two
+// One CTA per (256-query block, batch*head): two 128-query tiles that take turns on the tensor
+// pipe, so the softmax of one tile runs under the MMAs of the other. Memory stays O(S): K/V
+// stream through 2-stage shared-memory rings; scores, probabilities and the output accumulator
+// live in TMEM (512 columns: S0 | S1 | O0 | O1, 128 fp32 columns each).
+//   warp 0      TMA producer: both Q tiles once, then K_j / V_j tiles (128 keys x 128 dims, two
 //               128B-swizzled 64-wide boxes each), separate full/empty barriers for K and V.
-//   warp 1      MMA issuer: S_j = Q K_j^T (tcgen05.mma 128x128x16 x8) into one of two TMEM
-//               score buffers -- issued one block ahead so the tensor pipe works while the
-//               softmax of the previous block runs -- then PV_j = P_j V_j into a third
-//               TMEM buffer (V is the MN-major operand: no transposition).
-//   warps 2..5  softmax, one query row per thread: pass 1 reads S_j from TMEM for the row
-//               max; the previous block's PV tile is folded into the fp32 output row kept
-//               in registers and rescaled by exp2((m_old-m_new)*c); pass 2 re-reads S_j,
-//               p = exp2(s*c - m*c) with c = scale*log2(e), accumulates the row sum in
-//               fp32 and writes P_j as 16-bit values into 128B-swizzled shared memory, the
-//               A operand of the PV product.
-// Causal blocks above the diagonal are never loaded or multiplied; the diagonal block and
-// a ragged last key block are masked elementwise. Heavy (late) query blocks are scheduled
-// first. Every mbarrier wait is bounded.
+//   warp 1      MMA issuer, per key block j and tile t: PV(t,j) then QK(t,j+1).
+//               S_t = Q_t K_j^T is tcgen05.mma 128x128x16 x8 with both operands in shared memory;
+//               O_t += P_t V_j takes A = P_t from TMEM (16-bit values packed two per column, written
+//               by the softmax warps over the first 64 columns of S_t) and B = V_j MN-major.
+//   warps 2..9  softmax, four warps per tile, one query row per thread: ONE pass over the 128
+//               scores of the row in registers (max, exp2 with scale*log2(e) folded in, row sum,
+//               16-bit pack, tcgen05.st). The output accumulator is rescaled in TMEM only when the
+//               running maximum has grown by more than 2^8 since the last rescale (decided per
+//               warp), so on most blocks the accumulator is never touched by the softmax warps.
+// Causal blocks above the diagonal are never loaded or multiplied; the diagonal block and a
+// ragged last key block are masked elementwise. Heavy (late) query blocks are scheduled first.
+// Every mbarrier wait is bounded.
 #include <algorithm>
 
 #include "../common.h"
@@ -30,15 +31,16 @@ using namespace sm100;
 
 namespace {
 
-constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int BQ = 128, BKV = 128, HD = 128, QTILES = 2;
 constexpr int TILE_BYTES = 128 * 128 * 2;  // one 128x128 16-bit tile = two 64-wide boxes
 constexpr int HALF_BYTES = TILE_BYTES / 2; // one 128-row x 64-col swizzled box
-constexpr int SM_Q = 0, SM_K = TILE_BYTES, SM_V = 3 * TILE_BYTES, SM_P = 5 * TILE_BYTES;
+constexpr int SM_Q = 0, SM_K = 2 * TILE_BYTES, SM_V = 4 * TILE_BYTES;
 constexpr int SM_BARS = 6 * TILE_BYTES;
 constexpr int SMEM_BYTES = 6 * TILE_BYTES + 1024 + 256;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;
 constexpr int TMEM_COLS = 512;
-constexpr int TM_PV = 0, TM_S = 128; // PV tile: cols [0,128); score buffers: [128,256), [256,384)
+constexpr int TM_S = 0, TM_O = 256; // S_t: cols [128t, 128t+128); O_t: cols [256+128t, ...)
+constexpr float RESCALE_LOG2 = 8.f; // the accumulator is rescaled when the row max grew by > 2^8
 
 struct SdpaTcParams {
   int32_t B, Hq, Hk, Sq, Skv;
@@ -48,6 +50,21 @@ struct SdpaTcParams {
   void *out;
   uint32_t *err;
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t addr, const uint32_t *v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+        "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -61,9 +78,9 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto k_empty = [&](int s) { return bar_base + 8u * (3 + s); };
   auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
   auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
-  auto s_full = [&](int s) { return bar_base + 8u * (9 + s); };
-  auto s_empty = [&](int s) { return bar_base + 8u * (11 + s); };
-  const uint32_t p_full = bar_base + 8u * 13, pv_full = bar_base + 8u * 14;
+  auto s_full = [&](int t) { return bar_base + 8u * (9 + t); };
+  auto p_full = [&](int t) { return bar_base + 8u * (11 + t); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (13 + t); };
   const uint32_t tmem_slot = bar_base + 8u * 15;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -72,9 +89,16 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int bh = blockIdx.y;
   const int b = bh / p.Hq, h = bh % p.Hq;
   const int kvh = b * p.Hk + h / (p.Hq / p.Hk);
-  const int q0 = qb * BQ;
-  int nblk = (p.Skv + BKV - 1) / BKV;
-  if (p.causal) nblk = min(nblk, (q0 + BQ - 1) / BKV + 1);
+  const int q0 = qb * (BQ * QTILES);
+  const int nblk_all = (p.Skv + BKV - 1) / BKV;
+  // key blocks each tile needs; a tile that starts beyond Sq does nothing
+  int nt[QTILES];
+#pragma unroll
+  for (int t = 0; t < QTILES; ++t) {
+    const int qt = q0 + t * BQ;
+    nt[t] = qt >= p.Sq ? 0 : (p.causal ? min(nblk_all, (qt + BQ - 1) / BKV + 1) : nblk_all);
+  }
+  const int nmax = max(nt[0], nt[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -84,10 +108,9 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(s_empty(s), 4);
+      mbar_init(p_full(s), 4);
+      mbar_init(pv_done(s), 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_full, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -105,11 +128,14 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_3d(smem_base + SM_Q, &tmap_q, q_full, 0, q0, bh);
-      tma_load_3d(smem_base + SM_Q + HALF_BYTES, &tmap_q, q_full, 64, q0, bh);
+      mbar_expect_tx(q_full, QTILES * TILE_BYTES);
+#pragma unroll
+      for (int t = 0; t < QTILES; ++t) {
+        tma_load_3d(smem_base + SM_Q + t * TILE_BYTES, &tmap_q, q_full, 0, q0 + t * BQ, bh);
+        tma_load_3d(smem_base + SM_Q + t * TILE_BYTES + HALF_BYTES, &tmap_q, q_full, 64, q0 + t * BQ, bh);
+      }
       bool ok = true;
-      for (int j = 0; j < nblk && ok; ++j) {
+      for (int j = 0; j < nmax && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(k_empty(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -126,164 +152,164 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      // scores: A = Q (K-major), B = K_j (K-major, N = keys); output: A = P (K-major), B = V_j (MN-major)
+      // scores: A = Q_t (K-major), B = K_j (K-major, N = keys)
+      // output: A = P_t (TMEM), B = V_j (MN-major: 64-wide head-dim blocks HALF_BYTES apart,
+      //         8-key groups 1024 B apart)
       const uint32_t idesc_qk = make_idesc_f16(BQ, BKV, p.ab_format, 0, 0);
       const uint32_t idesc_pv = make_idesc_f16(BQ, HD, p.ab_format, 0, 1);
-      const uint32_t sq = smem_base + SM_Q, sp = smem_base + SM_P;
-      bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
-      auto issue_scores = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(k_full(s), ph, p.err, ERR_WAIT_FULL)) return false;
-        if (!mbar_wait(s_empty(s), ph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) return false;
-        tc_fence_after();
-        const uint32_t sk = smem_base + SM_K + s * TILE_BYTES;
+      auto issue_qk = [&](int t, int j) {
+        const uint32_t sq = smem_base + SM_Q + t * TILE_BYTES;
+        const uint32_t sk = smem_base + SM_K + (j & 1) * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_f16(tmem_base + TM_S + s * BKV, make_smem_desc(sq + off, 16, 1024),
+          tc_mma_f16(tmem_base + TM_S + t * BKV, make_smem_desc(sq + off, 16, 1024),
                      make_smem_desc(sk + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(k_empty(s));
-        tc_commit(s_full(s));
-        return true;
+        tc_commit(s_full(t));
       };
-      if (ok && nblk > 0) ok = issue_scores(0);
-      for (int j = 0; j < nblk && ok; ++j) {
-        if (j + 1 < nblk) {
-          if (!issue_scores(j + 1)) { ok = false; break; }
+      auto issue_pv = [&](int t, int j) {
+        const uint32_t sv = smem_base + SM_V + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          tc_mma_f16_ts(tmem_base + TM_O + t * HD, tmem_base + TM_S + t * BKV + k * 8,
+                        make_smem_desc(sv + k * 2048, HALF_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(pv_done(t));
+      };
+      bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
+      if (ok && nmax > 0) {
+        ok = mbar_wait(k_full(0), 0, p.err, ERR_WAIT_FULL);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int t = 0; t < QTILES; ++t)
+            if (nt[t] > 0) issue_qk(t, 0);
+          tc_commit(k_empty(0));
         }
+      }
+      for (int j = 0; j < nmax && ok; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(v_full(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-        if (!mbar_wait(p_full, j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t sv = smem_base + SM_V + s * TILE_BYTES;
+        if (j + 1 < nmax && !mbar_wait(k_full(s ^ 1), ((j + 1) >> 1) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          // V_j: 64-wide head-dim blocks HALF_BYTES apart (LBO), 8-key groups 1024 B apart
-          tc_mma_f16(tmem_base + TM_PV, make_smem_desc(sp + a_off, 16, 1024),
-                     make_smem_desc(sv + k * 2048, HALF_BYTES, 1024), idesc_pv, k > 0 ? 1u : 0u);
+        for (int t = 0; t < QTILES; ++t) {
+          if (j < nt[t]) {
+            if (!mbar_wait(p_full(t), j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, j);
+          }
+          if (j + 1 < nt[t]) issue_qk(t, j + 1);
         }
+        if (!ok) break;
         tc_commit(v_empty(s));
-        tc_commit(pv_full);
+        if (j + 1 < nmax) tc_commit(k_empty(s ^ 1));
       }
     }
   } else {
-    const int q = warp & 3;
+    const int t = (warp - 2) >> 2;     // query tile of this warp
+    const int q = warp & 3;            // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;
-    const int qi = q0 + row;
+    const int q0t = q0 + t * BQ;
+    const int qi = q0t + row;
+    const int n_blocks = nt[t];
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t s_addr = tmem_base + TM_S + t * BKV + lane_addr;
+    const uint32_t o_addr = tmem_base + TM_O + t * HD + lane_addr;
     const float c = p.scale_log2e;
-    float m_run = -INFINITY, l_run = 0.f;
-    float o_acc[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o_acc[d] = 0.f;
+    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    const uint32_t p_row = smem_base + SM_P + (uint32_t)row * 128u;
-    for (int j = 0; j < nblk && ok; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(s_full(s), ph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      if (!mbar_wait(s_full(t), j & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem_base + TM_S + s * BKV + lane_addr;
       const int k0 = j * BKV;
-      const bool need_mask = (k0 + BKV > p.Skv) || (p.causal && k0 + BKV - 1 > q0);
+      const bool need_mask = (k0 + BKV > p.Skv) || (p.causal && k0 + BKV - 1 > q0t);
       const int k_lim = p.causal ? min(p.Skv, qi + 1) : p.Skv; // keys >= k_lim are masked for this row
-      // pass 1: row maximum of the raw scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int cc = 0; cc < BKV / 32; ++cc) {
-        uint32_t raw[32];
-        tmem_ld_32x32(s_addr + cc * 32, raw);
-        tmem_ld_wait();
-        if (need_mask) {
+      // the whole score row of this block, one pass
+      uint32_t raw[BKV];
 #pragma unroll
-          for (int t = 0; t < 32; ++t)
-            if (k0 + cc * 32 + t < k_lim) mx = fmaxf(mx, __uint_as_float(raw[t]));
-        } else {
+      for (int cc = 0; cc < BKV / 32; ++cc) tmem_ld_32x32(s_addr + cc * 32, raw + cc * 32);
+      tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) mx = fmaxf(mx, __uint_as_float(raw[t]));
-        }
+        for (int i = 0; i < BKV; ++i)
+          if (k0 + i >= k_lim) raw[i] = 0xff800000u; // -inf
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f((m_run - m_use) * c); // exp2(-inf) = 0 on the first block
-      // fold in the previous block's P*V (computed against m_run), then rescale to m_new
-      if (j > 0) {
-        if (!mbar_wait(pv_full, (j - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-        tc_fence_after();
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int cc = 0; cc < HD / 32; ++cc) {
-          uint32_t raw[32];
-          tmem_ld_32x32(tmem_base + TM_PV + lane_addr + cc * 32, raw);
-          tmem_ld_wait();
-#pragma unroll
-          for (int t = 0; t < 32; ++t) o_acc[cc * 32 + t] = (o_acc[cc * 32 + t] + __uint_as_float(raw[t])) * alpha;
-        }
+      for (int i = 0; i < BKV; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(raw[i]));
+        mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
       }
-      l_run *= alpha;
-      m_run = m_new;
-      const float mc = m_use * c;
-      // pass 2: probabilities -> 16-bit -> swizzled shared memory
-      float lsum = 0.f;
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // Rescale only when some row of the warp moved its maximum by more than 2^RESCALE_LOG2
+      // (always on the first block): until then probabilities are taken against the stale
+      // maximum and stay below 2^RESCALE_LOG2, which fp32 sums and 16-bit P hold exactly as well.
+      const bool grow = mx > m_ref && ((mx - m_ref) * c > RESCALE_LOG2 || m_ref == -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new; // a fully masked row so far
+        const float alpha = (m_ref == -INFINITY) ? 0.f : ex2_approx((m_ref - m_use) * c);
+        if (j > 0) {
+          if (!mbar_wait(pv_done(t), (j - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll 1
+          for (int cc = 0; cc < HD / 32; ++cc) {
+            uint32_t acc[32];
+            tmem_ld_32x32(o_addr + cc * 32, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+            tmem_st_32x32(o_addr + cc * 32, acc);
+          }
+        }
+        l_run *= alpha;
+        m_ref = (m_new == -INFINITY) ? -INFINITY : m_use;
+      }
+      const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
+      // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
       for (int cc = 0; cc < BKV / 32; ++cc) {
-        uint32_t raw[32];
-        tmem_ld_32x32(s_addr + cc * 32, raw);
-        tmem_ld_wait();
         uint32_t packed[16];
 #pragma unroll
-        for (int t = 0; t < 16; ++t) {
-          float p0 = exp2f(fmaf(__uint_as_float(raw[2 * t]), c, -mc));
-          float p1 = exp2f(fmaf(__uint_as_float(raw[2 * t + 1]), c, -mc));
-          if (need_mask) {
-            if (k0 + cc * 32 + 2 * t >= k_lim) p0 = 0.f;
-            if (k0 + cc * 32 + 2 * t + 1 >= k_lim) p1 = 0.f;
-          }
-          lsum += p0 + p1;
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(raw[cc * 32 + 2 * i]), c, -mc));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(raw[cc * 32 + 2 * i + 1]), c, -mc));
+          l0 += p0;
+          l1 += p1;
           if (p.ab_format) {
             __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-            packed[t] = *reinterpret_cast<uint32_t *>(&hh);
+            packed[i] = *reinterpret_cast<uint32_t *>(&hh);
           } else {
             __half2 hh = __floats2half2_rn(p0, p1);
-            packed[t] = *reinterpret_cast<uint32_t *>(&hh);
+            packed[i] = *reinterpret_cast<uint32_t *>(&hh);
           }
         }
-        // 32 keys = four 16-byte chunks of this row; chunk index XOR (row % 8) is the 128B swizzle
-        const uint32_t half_base = p_row + (uint32_t)(cc >> 1) * HALF_BYTES;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const uint32_t chunk = (uint32_t)((cc & 1) * 4 + ch) ^ (uint32_t)(row & 7);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(half_base + chunk * 16u),
-                       "r"(packed[4 * ch]), "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
-                       : "memory");
-        }
+        tmem_st_32x16(s_addr + cc * 16, packed);
       }
-      l_run += lsum;
-      // scores consumed: the score buffer may be overwritten; P written: publish to the tensor proxy
+      l_run += l0 + l1;
+      tmem_st_wait();
+      // P (and a rescaled accumulator) are in TMEM: let the MMA warp issue P V
       tc_fence_before();
-      fence_proxy_async();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty(s));
-        mbar_arrive(p_full);
-      }
+      if (lane == 0) mbar_arrive(p_full(t));
     }
-    if (ok && nblk > 0) {
-      if (mbar_wait(pv_full, (nblk - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) {
+    if (ok && n_blocks > 0) {
+      if (mbar_wait(pv_done(t), (n_blocks - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) {
         tc_fence_after();
         const float inv = 1.f / l_run;
         const int64_t row_off = ((int64_t)bh * p.Sq + qi) * HD;
-#pragma unroll
+#pragma unroll 1
         for (int cc = 0; cc < HD / 32; ++cc) {
-          uint32_t raw[32];
-          tmem_ld_32x32(tmem_base + TM_PV + lane_addr + cc * 32, raw);
+          uint32_t acc[32];
+          tmem_ld_32x32(o_addr + cc * 32, acc);
           tmem_ld_wait();
           float v[32];
 #pragma unroll
-          for (int t = 0; t < 32; ++t) v[t] = (o_acc[cc * 32 + t] + __uint_as_float(raw[t])) * inv;
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * inv;
           if (qi < p.Sq) epi_store32(p.out, p.out_dtype, row_off + cc * 32, v, 32);
         }
       }
@@ -319,6 +345,7 @@ bool sdpa_tc_eligible(const Plan &p, const Step &s) {
   if (q.dims[2] < 128 || k.dims[2] < 128) return false; // short sequences: CUDA-core kernel
   if (q.dims[0] * q.dims[1] > 65535) return false;
   if (d.fparams[1] != 0.f) return false;
+  if ((d.flags & FB_FLAG_SDPA_HAS_SCALE) && !(d.fparams[0] > 0.f)) return false; // max(s) must be max(s*scale)
   return true;
 }
 
@@ -339,7 +366,7 @@ fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s) {
   p.causal = (d.flags & FB_FLAG_SDPA_CAUSAL) ? 1 : 0;
   p.ab_format = q.dtype == FB_DT_BFLOAT16 ? 1 : 0;
   p.out_dtype = q.dtype;
-  p.q_blocks = (p.Sq + BQ - 1) / BQ;
+  p.q_blocks = (p.Sq + BQ * QTILES - 1) / (BQ * QTILES);
   const float scale = (d.flags & FB_FLAG_SDPA_HAS_SCALE) ? d.fparams[0] : 1.f / sqrtf((float)HD);
   p.scale_log2e = scale * 1.4426950408889634f;
   p.out = op;

@@ -136,10 +136,27 @@ def test_matmul_batch_broadcast_and_transposed_a():
     dict(b=2, h=4, s=512, d=128, dtype=BF16, causal=True),
     dict(b=1, h=2, s=384, d=128, dtype=BF16, causal=False),
     dict(b=1, h=2, s=200, d=128, dtype=BF16, causal=True),
+    dict(b=1, h=4, s=1024, d=128, dtype=BF16, causal=True, hkv=2),
+    dict(b=1, h=2, s=640, d=128, dtype=F16, causal=False),
+    dict(b=1, h=2, s=300, d=128, dtype=BF16, causal=False, skv=1000),
+    dict(b=1, h=1, s=1280, d=128, dtype=BF16, causal=True, scale=0.5),
 ])
 def test_sdpa(cfg):
     g, ins, _ = wl.sdpa_fwd(**cfg)
     data = _inputs(ins, 21, ("normal", 0.0, 1.0))
+    check_graph(g, data)
+
+
+def test_sdpa_growing_row_maximum():
+    """Scores whose row maximum keeps rising along the key axis (keys scaled by their index), so the
+    accumulator rescaling in the tensor-core kernel runs on many blocks, not only on the first."""
+    g, ins, _ = wl.sdpa_fwd(b=1, h=2, s=1024, d=128, dtype=BF16, causal=False)
+    data = _inputs(ins, 22, ("normal", 0.0, 1.0))
+    from oracle import fusilli_oracle as orc
+    k = ins["k"]
+    kv = orc.from_storage(data[k], BF16).reshape(1, 2, 1024, 128)
+    ramp = np.linspace(0.2, 4.0, 1024, dtype=np.float32).reshape(1, 1, 1024, 1)
+    data[k] = orc.to_storage((kv * ramp).reshape(-1).astype(np.float32), BF16)
     check_graph(g, data)
 
 

@@ -57,6 +57,38 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// packed fp32 pairs: one instruction per pair on sm_100
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<uint64_t *>(&d))
+      : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)),
+        "l"(*reinterpret_cast<uint64_t *>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<uint64_t *>(&d))
+      : "l"(*reinterpret_cast<uint64_t *>(&a)), "l"(*reinterpret_cast<uint64_t *>(&b)));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void tmem_st_32x16(uint32_t addr, const uint32_t *v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -79,9 +111,10 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   auto v_full = [&](int s) { return bar_base + 8u * (5 + s); };
   auto v_empty = [&](int s) { return bar_base + 8u * (7 + s); };
   auto s_full = [&](int t) { return bar_base + 8u * (9 + t); };
-  auto p_full = [&](int t) { return bar_base + 8u * (11 + t); };
-  auto pv_done = [&](int t) { return bar_base + 8u * (13 + t); };
-  const uint32_t tmem_slot = bar_base + 8u * 15;
+  // P_t is published in two halves (keys 0..63, 64..127) so that P V starts under the second half's exp
+  auto p_half = [&](int t, int hf) { return bar_base + 8u * (11 + 2 * t + hf); };
+  auto pv_done = [&](int t) { return bar_base + 8u * (15 + t); };
+  const uint32_t tmem_slot = bar_base + 8u * 17;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // heavy query blocks (late rows under a causal mask) first
@@ -92,12 +125,11 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int q0 = qb * (BQ * QTILES);
   const int nblk_all = (p.Skv + BKV - 1) / BKV;
   // key blocks each tile needs; a tile that starts beyond Sq does nothing
-  int nt[QTILES];
-#pragma unroll
-  for (int t = 0; t < QTILES; ++t) {
+  auto blocks_of = [&](int t) {
     const int qt = q0 + t * BQ;
-    nt[t] = qt >= p.Sq ? 0 : (p.causal ? min(nblk_all, (qt + BQ - 1) / BKV + 1) : nblk_all);
-  }
+    return qt >= p.Sq ? 0 : (p.causal ? min(nblk_all, (qt + BQ - 1) / BKV + 1) : nblk_all);
+  };
+  const int nt[QTILES] = {blocks_of(0), blocks_of(1)};
   const int nmax = max(nt[0], nt[1]);
 
   if (threadIdx.x == 0) {
@@ -108,7 +140,8 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(v_full(s), 1);
       mbar_init(v_empty(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(p_full(s), 4);
+      mbar_init(p_half(s, 0), 4);
+      mbar_init(p_half(s, 1), 4);
       mbar_init(pv_done(s), 1);
     }
     fence_barrier_init();
@@ -151,57 +184,73 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // scores: A = Q_t (K-major), B = K_j (K-major, N = keys)
-      // output: A = P_t (TMEM), B = V_j (MN-major: 64-wide head-dim blocks HALF_BYTES apart,
-      //         8-key groups 1024 B apart)
-      const uint32_t idesc_qk = make_idesc_f16(BQ, BKV, p.ab_format, 0, 0);
-      const uint32_t idesc_pv = make_idesc_f16(BQ, HD, p.ab_format, 0, 1);
-      auto issue_qk = [&](int t, int j) {
-        const uint32_t sq = smem_base + SM_Q + t * TILE_BYTES;
-        const uint32_t sk = smem_base + SM_K + (j & 1) * TILE_BYTES;
+    // The whole warp runs the loop so that addresses and descriptors stay in uniform registers;
+    // one elected lane issues the MMAs and the commits (a commit tracks the issuing thread).
+    const bool leader = elect_one();
+    // scores: A = Q_t (K-major), B = K_j (K-major, N = keys)
+    // output: A = P_t (TMEM), B = V_j (MN-major: 64-wide head-dim blocks HALF_BYTES apart,
+    //         8-key groups 1024 B apart)
+    const uint32_t idesc_qk = make_idesc_f16(BQ, BKV, p.ab_format, 0, 0);
+    const uint32_t idesc_pv = make_idesc_f16(BQ, HD, p.ab_format, 0, 1);
+    // descriptor of the first K-step of each operand; later K-steps add a constant to the
+    // 16-byte-unit address field
+    const uint64_t q_desc0 = make_smem_desc(smem_base + SM_Q, 16, 1024);
+    const uint64_t k_desc0 = make_smem_desc(smem_base + SM_K, 16, 1024);
+    const uint64_t v_desc0 = make_smem_desc(smem_base + SM_V, HALF_BYTES, 1024);
+    auto issue_qk = [&](int t, int j) {
+      const uint64_t qd = q_desc0 + (uint64_t)((t * TILE_BYTES) >> 4);
+      const uint64_t kd = k_desc0 + (uint64_t)(((j & 1) * TILE_BYTES) >> 4);
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          tc_mma_f16(tmem_base + TM_S + t * BKV, make_smem_desc(sq + off, 16, 1024),
-                     make_smem_desc(sk + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
+          tc_mma_f16(tmem_base + TM_S + t * BKV, qd + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
         }
         tc_commit(s_full(t));
-      };
-      auto issue_pv = [&](int t, int j) {
-        const uint32_t sv = smem_base + SM_V + (j & 1) * TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < BKV / 16; ++k)
-          tc_mma_f16_ts(tmem_base + TM_O + t * HD, tmem_base + TM_S + t * BKV + k * 8,
-                        make_smem_desc(sv + k * 2048, HALF_BYTES, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(pv_done(t));
-      };
-      bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
-      if (ok && nmax > 0) {
-        ok = mbar_wait(k_full(0), 0, p.err, ERR_WAIT_FULL);
-        if (ok) {
-          tc_fence_after();
-#pragma unroll
-          for (int t = 0; t < QTILES; ++t)
-            if (nt[t] > 0) issue_qk(t, 0);
-          tc_commit(k_empty(0));
-        }
       }
-      for (int j = 0; j < nmax && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(v_full(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-        if (j + 1 < nmax && !mbar_wait(k_full(s ^ 1), ((j + 1) >> 1) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+    };
+    auto issue_pv = [&](int t, int j, int hf) {
+      const uint64_t vd = v_desc0 + (uint64_t)(((j & 1) * TILE_BYTES) >> 4);
+      if (leader) {
 #pragma unroll
-        for (int t = 0; t < QTILES; ++t) {
-          if (j < nt[t]) {
-            if (!mbar_wait(p_full(t), j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, j);
-          }
-          if (j + 1 < nt[t]) issue_qk(t, j + 1);
+        for (int kk = 0; kk < BKV / 32; ++kk) {
+          const int k = hf * (BKV / 32) + kk;
+          tc_mma_f16_ts(tmem_base + TM_O + t * HD, tmem_base + TM_S + t * BKV + k * 8,
+                        vd + (uint64_t)((k * 2048) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        if (!ok) break;
+        if (hf == 1) tc_commit(pv_done(t));
+      }
+    };
+    bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
+    if (ok && nmax > 0) {
+      ok = mbar_wait(k_full(0), 0, p.err, ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < QTILES; ++t)
+          if (nt[t] > 0) issue_qk(t, 0);
+        if (leader) tc_commit(k_empty(0));
+      }
+    }
+    for (int j = 0; j < nmax && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(v_full(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+      if (j + 1 < nmax && !mbar_wait(k_full(s ^ 1), ((j + 1) >> 1) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+#pragma unroll
+      for (int t = 0; t < QTILES; ++t) {
+        if (j < nt[t]) {
+          if (!mbar_wait(p_half(t, 0), j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, j, 0);
+          if (!mbar_wait(p_half(t, 1), j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, j, 1);
+        }
+        if (j + 1 < nt[t]) issue_qk(t, j + 1);
+      }
+      if (!ok) break;
+      if (leader) {
         tc_commit(v_empty(s));
         if (j + 1 < nmax) tc_commit(k_empty(s ^ 1));
       }
@@ -212,7 +261,7 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int row = q * 32 + lane;
     const int q0t = q0 + t * BQ;
     const int qi = q0t + row;
-    const int n_blocks = nt[t];
+    const int n_blocks = t ? nt[1] : nt[0];
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t s_addr = tmem_base + TM_S + t * BKV + lane_addr;
     const uint32_t o_addr = tmem_base + TM_O + t * HD + lane_addr;
@@ -237,11 +286,11 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < BKV; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(raw[i]));
-        mx1 = fmaxf(mx1, __uint_as_float(raw[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(raw[i + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(raw[i + 3]));
+      for (int i = 0; i < BKV; i += 8) {
+        mx0 = max3(mx0, __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+        mx1 = max3(mx1, __uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3]));
+        mx2 = max3(mx2, __uint_as_float(raw[i + 4]), __uint_as_float(raw[i + 5]));
+        mx3 = max3(mx3, __uint_as_float(raw[i + 6]), __uint_as_float(raw[i + 7]));
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       // Rescale only when some row of the warp moved its maximum by more than 2^RESCALE_LOG2
@@ -270,32 +319,40 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
       // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
-      float l0 = 0.f, l1 = 0.f;
+      // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
+      const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
+      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
 #pragma unroll
       for (int cc = 0; cc < BKV / 32; ++cc) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(raw[cc * 32 + 2 * i]), c, -mc));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(raw[cc * 32 + 2 * i + 1]), c, -mc));
-          l0 += p0;
-          l1 += p1;
+          const float2 x = f2_fma(make_float2(__uint_as_float(raw[cc * 32 + 2 * i]), __uint_as_float(raw[cc * 32 + 2 * i + 1])),
+                                  c2, nmc2);
+          float2 pr;
+          pr.x = ex2_approx(x.x);
+          pr.y = ex2_approx(x.y);
+          if (i & 1) lb = f2_add(lb, pr);
+          else la = f2_add(la, pr);
           if (p.ab_format) {
-            __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+            __nv_bfloat162 hh = __floats2bfloat162_rn(pr.x, pr.y);
             packed[i] = *reinterpret_cast<uint32_t *>(&hh);
           } else {
-            __half2 hh = __floats2half2_rn(p0, p1);
+            __half2 hh = __floats2half2_rn(pr.x, pr.y);
             packed[i] = *reinterpret_cast<uint32_t *>(&hh);
           }
         }
         tmem_st_32x16(s_addr + cc * 16, packed);
+        if (cc & 1) {
+          // half of P (and, the first time, a rescaled accumulator) is in TMEM: let the MMA warp
+          // issue that half of P V
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_half(t, cc >> 1));
+        }
       }
-      l_run += l0 + l1;
-      tmem_st_wait();
-      // P (and a rescaled accumulator) are in TMEM: let the MMA warp issue P V
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(t));
+      l_run += (la.x + la.y) + (lb.x + lb.y);
     }
     if (ok && n_blocks > 0) {
       if (mbar_wait(pv_done(t), (n_blocks - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) {

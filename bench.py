@@ -213,7 +213,8 @@ def side_configs(torch, fz, wl, handle, pk):
     y1 = torch.empty(16, 56, 56, 64, device="cuda")
     g, ins, o = wl.conv_fprop_bias_relu(16, 64, 56, 56, 64, 3, 3, 1, DataType.Float)
     run("C1_conv_fprop_f32_16x56x56x64_k64_3x3_bias_relu", g, ins, [(o, y1)], {"x": x1, "w": w1, "bias": b1},
-        2.0 * 16 * 56 * 56 * 64 * 64 * 9, "TFLOP/s", pk["tf_burst"], "tensor (fp32-accurate CUDA-core path)", flush=flush)
+        2.0 * 16 * 56 * 56 * 64 * 64 * 9, "TFLOP/s", 148 * 128 * 2 * 1.965e-3,
+        "fp32 FFMA (CUDA cores; nominal 148 SMs x 128 lanes x 2 x 1.965 GHz, fp32 results to rtol 1e-5)", flush=flush)
     # C3: SDPA fwd bf16 B8 H32 S4096 D128 causal
     try:
         q = torch.randn(8, 32, 4096, 128, device="cuda").to(bf)

@@ -1,14 +1,18 @@
 // LayerNorm (inference and training outputs) and RMSNorm over all non-batch dims.
 //
-// X is contiguous or channels-last, so each sample is one dense run of R
-// elements; one CTA owns one sample. HBM-bound: the row kernel reads the row once
-// with 128-bit loads into registers, reduces in fp32 (warp shuffles + shared
-// memory), and writes once -- 2 * R * sizeof(T) bytes of traffic per row, the
-// algorithmic minimum. Statistics are two-pass over the register copy (mean, then
-// centred sum of squares), so there is no cancellation. The generic kernel
-// re-reads the row from L2 instead and handles any row length and layouts where
-// scale/bias/Y are ordered differently from X.
+// X is contiguous or channels-last, so each sample is one dense run of R elements ("row").
+// HBM-bound: every kernel reads a row once and writes it once -- 2 * R * sizeof(T) bytes per
+// row, the algorithmic minimum -- and takes the statistics in ONE block reduction through shifted
+// moments: d = x - x0 (x0 = first element of the row), mean = x0 + sum(d)/R,
+// var = sum(d*d)/R - (sum(d)/R)^2, which has none of the cancellation of E[x^2] - mean^2.
+//   norm_rows_staged_kernel  LayerNorm on long rows with many samples: persistent CTAs, rows
+//                            staged through a shared-memory ring by bulk copies, scale and bias
+//                            in registers;
+//   norm_rows_kernel         one row per CTA, the row packed in registers, parameters through L1;
+//   norm_generic_kernel      any row length and layouts where scale/bias/Y are ordered
+//                            differently from X (re-reads the row from L2).
 #include "../common.h"
+#include "sm100.cuh"
 
 namespace fb {
 
@@ -24,6 +28,7 @@ struct NormParams {
   int64_t inner_dims[FB_MAX_RANK]; // non-batch dims in X's physical order, slowest first
   int64_t y_istr[FB_MAX_RANK], s_istr[FB_MAX_RANK], b_istr[FB_MAX_RANK];
   int32_t same_order; // Y, scale, bias are all laid out like X within a row
+  uint32_t *err;      // device error word for bounded waits
 };
 
 __device__ __forceinline__ float block_sum(float v, float *smem) {
@@ -249,9 +254,163 @@ __global__ void __launch_bounds__(THREADS) norm_rows_kernel(const NormParams p) 
   }
 }
 
+// Staged row kernel for the large-row case (HBM-bound at full speed): persistent CTAs of 256
+// threads, each walking rows blockIdx.x, blockIdx.x + gridDim.x, ... The rows arrive through a
+// ring of STAGES shared-memory slots filled by bulk copies (cp.async.bulk, one elected thread,
+// completion on an mbarrier), so STAGES rows per CTA are in flight whatever the threads are
+// doing; scale and bias live in registers for the whole kernel (no per-row parameter traffic);
+// one barrier per row (partial sums double-buffered). T = X and Y element type, P = scale/bias
+// element type, V 16-byte vectors per thread (row == 256 * V * (16 / sizeof(T))).
+constexpr int kStagedStages = 4;
+template <typename T, typename P, int V, int THREADS>
+__global__ void __launch_bounds__(THREADS, 2) norm_rows_staged_kernel(const NormParams p) {
+  using namespace sm100;
+  constexpr int STAGES = kStagedStages;
+  constexpr int N = 16 / sizeof(T), NP = N / 2, NW = THREADS / 32;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  const uint32_t row_bytes = (uint32_t)(p.row * sizeof(T));
+  const uint32_t smem0 = smem_u32(smem_raw);
+  const uint32_t bar0 = smem0 + STAGES * row_bytes;
+  float2 *partial = reinterpret_cast<float2 *>(smem_raw + STAGES * row_bytes + 64); // [2][NW]
+  const int64_t first = blockIdx.x, step = gridDim.x;
+  const int64_t my_rows = first < p.batch ? (p.batch - first + step - 1) / step : 0;
+  auto issue = [&](int64_t k) { // row k of this CTA into slot k % STAGES
+    const uint32_t bar = bar0 + 8u * (uint32_t)(k % STAGES);
+    mbar_expect_tx(bar, row_bytes);
+    tma_bulk_load(smem0 + (uint32_t)(k % STAGES) * row_bytes,
+                  static_cast<const T *>(p.x) + (first + k * step) * p.x_bstride, row_bytes, bar);
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
+    fence_barrier_init();
+    for (int64_t k = 0; k < STAGES && k < my_rows; ++k) issue(k);
+  }
+  // parameters of this thread's columns, once
+  float2 g[V * NP], bt[V * NP];
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int64_t col = ((int64_t)threadIdx.x + v * THREADS) * N;
+    float gf[N], bf[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      gf[j] = 1.f;
+      bf[j] = 0.f;
+    }
+    if (p.scale) load_params<P, N>(p.scale, col, gf);
+    if (p.bias) load_params<P, N>(p.bias, col, bf);
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      g[v * NP + j] = make_float2(gf[2 * j], gf[2 * j + 1]);
+      bt[v * NP + j] = make_float2(bf[2 * j], bf[2 * j + 1]);
+    }
+  }
+  __syncthreads(); // barriers initialised
+  const float inv_row = 1.f / (float)p.row;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int64_t k = 0; k < my_rows; ++k) {
+    const int slot = (int)(k % STAGES);
+    if (!mbar_wait(bar0 + 8u * slot, (uint32_t)((k / STAGES) & 1), p.err, ERR_WAIT_FULL)) break;
+    const uint4 *xr = reinterpret_cast<const uint4 *>(smem_raw + (size_t)slot * row_bytes);
+    uint4 raw[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) raw[v] = xr[threadIdx.x + v * THREADS];
+    const float x0 = p.is_rms ? 0.f : nelem_f<T>(*reinterpret_cast<const T *>(xr));
+    const float2 shift = make_float2(-x0, -x0);
+    float2 s2 = make_float2(0.f, 0.f), ss2 = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float2 d = f2_add(vec_pair<T>(raw[v], j), shift);
+        s2 = f2_add(s2, d);
+        ss2 = f2_fma(d, d, ss2);
+      }
+    }
+    float2 tot = make_float2(s2.x + s2.y, ss2.x + ss2.y);
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) {
+      tot.x += __shfl_xor_sync(0xffffffffu, tot.x, m);
+      tot.y += __shfl_xor_sync(0xffffffffu, tot.y, m);
+    }
+    float2 *part = partial + (k & 1) * NW;
+    if (lane == 0) part[warp] = tot;
+    __syncthreads(); // partial sums visible; every thread has also finished reading the slot
+    // The slot's reads have completed (their values fed the sums above) and the barrier orders
+    // them before this point, so the slot can be handed back to the copy engine.
+    if (threadIdx.x == 0 && k + STAGES < my_rows) issue(k + STAGES);
+    tot = part[lane & (NW - 1)]; // NW is a power of two: every group of NW lanes holds all partials
+#pragma unroll
+    for (int m = NW / 2; m >= 1; m >>= 1) {
+      tot.x += __shfl_xor_sync(0xffffffffu, tot.x, m);
+      tot.y += __shfl_xor_sync(0xffffffffu, tot.y, m);
+    }
+    float mean = 0.f, var;
+    if (p.is_rms) {
+      var = tot.y * inv_row;
+    } else {
+      const float ds = tot.x * inv_row;
+      mean = x0 + ds;
+      var = fmaxf(tot.y * inv_row - ds * ds, 0.f);
+    }
+    const float rstd = rsqrtf(var + p.eps);
+    const float2 rs2 = make_float2(rstd, rstd), nmr2 = make_float2(-mean * rstd, -mean * rstd);
+    const int64_t b = first + k * step;
+    uint4 *yr = reinterpret_cast<uint4 *>(static_cast<T *>(p.y) + b * p.y_bstride);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      uint4 o;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        // y = ((x - mean) * rstd) * gamma + beta, with (x*rstd - mean*rstd) as one fma
+        const float2 nrm = f2_fma(vec_pair<T>(raw[v], j), rs2, nmr2);
+        vec_set_pair<T>(o, j, f2_fma(nrm, g[v * NP + j], bt[v * NP + j]));
+      }
+      yr[threadIdx.x + v * THREADS] = o;
+    }
+    if (threadIdx.x == 0) {
+      if (p.mean) store_f(p.mean, p.mean_dtype, b, mean);
+      if (p.rstd) store_f(p.rstd, p.rstd_dtype, b, rstd);
+    }
+  }
+}
+
+template <typename T, typename P, int V, int THREADS>
+static bool launch_staged_v(const NormParams &p, int sm_count, cudaStream_t st) {
+  const size_t smem = (size_t)kStagedStages * p.row * sizeof(T) + 64 + 2 * (THREADS / 32) * sizeof(float2);
+  static bool configured = false; // per instantiation
+  if (!configured) {
+    if (cudaFuncSetAttribute(norm_rows_staged_kernel<T, P, V, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    configured = true;
+  }
+  const int blocks = (int)std::min<int64_t>(p.batch, (int64_t)sm_count * 2);
+  norm_rows_staged_kernel<T, P, V, THREADS><<<blocks, THREADS, smem, st>>>(p);
+  return true;
+}
+
+// Rows of exactly 256 * V vectors with V in {2, 4} and at least a few rows per CTA.
+template <typename T, typename P>
+static bool launch_staged(const NormParams &p, int sm_count, cudaStream_t st) {
+  constexpr int N = 16 / sizeof(T);
+  if (p.batch < (int64_t)sm_count * 4) return false;
+  if ((size_t)kStagedStages * p.row * sizeof(T) > 100 * 1024) return false; // two CTAs per SM
+  if (p.row % (256 * N) != 0) return false;
+  switch (p.row / (256 * N)) {
+  case 2: return launch_staged_v<T, P, 2, 256>(p, sm_count, st);
+  case 4: return launch_staged_v<T, P, 4, 256>(p, sm_count, st);
+  default: return false;
+  }
+}
+
 template <typename T, typename P>
 static bool launch_rows(const NormParams &p, int sm_count, cudaStream_t st) {
   constexpr int N = 16 / sizeof(T);
+  // LayerNorm: the staged kernel (scale and bias in registers); RMSNorm has half the parameter
+  // traffic and is faster on the one-row-per-CTA kernel below, which runs more warps per SM
+  if (!p.is_rms && launch_staged<T, P>(p, sm_count, st)) return true;
   const int blocks = (int)std::min<int64_t>(p.batch, (int64_t)sm_count * 64);
   if (p.row % (128 * N) == 0 && p.row / (128 * N) <= 8) {
     switch (p.row / (128 * N)) {
@@ -340,6 +499,7 @@ fb_status launch_norm(const ExecContext &cx, const Step &s) {
       if (x.dims[dd] > 1 && p.b_istr[i] != x.strides[dd]) p.same_order = 0;
     }
   }
+  p.err = cx.dev->error_word;
   cudaStream_t st = cx.dev->stream;
   int blocks = (int)std::min<int64_t>(p.batch, (int64_t)cx.dev->sm_count * 32);
   bool aligned = ((uintptr_t)p.x % 16 == 0) && ((uintptr_t)p.y % 16 == 0) &&

@@ -170,6 +170,23 @@ def test_layernorm_rows(dtype, rows, cols, pdt, train):
     check_graph(g, data, scale_atol=4.0 if dtype == F32 else 1.0)
 
 
+@pytest.mark.parametrize("kind,dtype,rows,cols,pdt,train", [
+    ("ln", BF16, 1500, 8192, F32, False), ("ln", BF16, 1201, 8192, F32, True), ("rms", BF16, 1500, 8192, F32, False),
+    ("ln", F16, 1333, 4096, F16, False), ("ln", F32, 1250, 4096, F32, True), ("rms", F32, 1400, 2048, F32, False),
+])
+def test_norm_many_rows(kind, dtype, rows, cols, pdt, train):
+    """Enough rows for the persistent, bulk-copy-staged row kernel (several rows per CTA, uneven
+    split over the grid)."""
+    if kind == "ln":
+        g, ins, _ = wl.layernorm_infer(rows, cols, dtype, pdt, train)
+        per = {"gamma": ("normal", 1.0, 0.02), "beta": ("normal", 0.0, 0.02)}
+    else:
+        g, ins, _ = wl.rmsnorm_infer(rows, cols, dtype)
+        per = {"gamma": ("normal", 1.0, 0.02)}
+    data = _inputs(ins, 33, ("normal", 0.5, 1.0), per=per)
+    check_graph(g, data, scale_atol=4.0 if dtype == F32 else 1.0)
+
+
 @pytest.mark.parametrize("dtype,rows,cols", [(BF16, 64, 8192), (F32, 7, 333)])
 def test_rmsnorm_rows(dtype, rows, cols):
     g, ins, _ = wl.rmsnorm_infer(rows, cols, dtype)

@@ -79,16 +79,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 __device__ __forceinline__ void tmem_st_32x16(uint32_t addr, const uint32_t *v) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "

@@ -138,6 +138,16 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
       ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One lane of a converged warp (the same lane every time for a given mask).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base+t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t addr, uint32_t *v) {
   asm volatile(

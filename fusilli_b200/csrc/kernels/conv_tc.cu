@@ -121,33 +121,36 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 0, p.dgrad);
-      const uint32_t b_lbo = p.dgrad ? 64 * BK * 2 : 16, b_kstep = p.dgrad ? 2048 : 32;
-      uint32_t it = 0, lt = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
-        const int acc = lt & 1;
-        const uint32_t aph = (lt >> 1) & 1;
-        if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+    // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
+    // elected lane issues the MMAs and the commits, which track the issuing thread.
+    const bool leader = elect_one();
+    const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 0, p.dgrad);
+    const uint32_t b_lbo = p.dgrad ? 64 * BK * 2 : 16, b_kstep = p.dgrad ? 2048 : 32;
+    const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
+    const uint64_t b_desc0 = make_smem_desc(smem_base + A_BYTES, b_lbo, 1024);
+    uint32_t it = 0, lt = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+      const int acc = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * MAX_BN;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * MAX_BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+        const uint64_t soff = (uint64_t)((s * STAGE_BYTES) >> 4);
+        if (leader) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = make_smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t bdesc = make_smem_desc(sb + k * b_kstep, b_lbo, 1024);
-            tc_mma_f16(d_tmem, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 16; ++k)
+            tc_mma_f16(d_tmem, a_desc0 + soff + (uint64_t)((k * 32) >> 4),
+                       b_desc0 + soff + (uint64_t)((k * b_kstep) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit(empty_bar(s));
         }
-        if (ok) tc_commit(tfull_bar(acc));
       }
+      if (ok && leader) tc_commit(tfull_bar(acc));
     }
   } else {
     const int q = warp & 3;

@@ -114,32 +114,36 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 1, 1);
-      uint32_t ia = 0, ib = 0;
-      bool ok = true;
-      for (int pi = 0; pi < npatch && ok; ++pi, ++ia) {
-        const int sa_i = ia % A_STAGES;
-        if (!mbar_wait(a_full(sa_i), (ia / A_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-        const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
-        for (int t = 0; t < ntaps; ++t, ++ib) {
-          const int sb_i = ib % B_STAGES;
-          if (!mbar_wait(b_full(sb_i), (ib / B_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
+    // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
+    // elected lane issues the MMAs and the commits, which track the issuing thread.
+    const bool leader = elect_one();
+    const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 1, 1);
+    // both tiles MN-major: 64-channel blocks HALF apart (LBO), 8-pixel groups 1024 B apart,
+    // a 16-pixel K step is 2048 B
+    const uint64_t a_desc0 = make_smem_desc(smem_base, HALF, 1024);
+    const uint64_t b_desc0 = make_smem_desc(sb_base, HALF, 1024);
+    uint32_t ia = 0, ib = 0;
+    bool ok = true;
+    for (int pi = 0; pi < npatch && ok; ++pi, ++ia) {
+      const int sa_i = ia % A_STAGES;
+      if (!mbar_wait(a_full(sa_i), (ia / A_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+      const uint64_t ad = a_desc0 + (uint64_t)((sa_i * A_STAGE_BYTES) >> 4);
+      for (int t = 0; t < ntaps; ++t, ++ib) {
+        const int sb_i = ib % B_STAGES;
+        if (!mbar_wait(b_full(sb_i), (ib / B_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t bd = b_desc0 + (uint64_t)((sb_i * B_STAGE_BYTES) >> 4);
+        if (leader) {
 #pragma unroll
-          for (int k = 0; k < KPIX / 16; ++k) {
-            // both tiles MN-major: 64-channel blocks HALF apart (LBO), 8-pixel groups 1024 B apart,
-            // a 16-pixel K step is 2048 B
-            tc_mma_f16(tmem_base + t * p.BN, make_smem_desc(sa + k * 2048, HALF, 1024),
-                       make_smem_desc(sb + k * 2048, HALF, 1024), idesc, (pi > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < KPIX / 16; ++k)
+            tc_mma_f16(tmem_base + t * p.BN, ad + (uint64_t)((k * 2048) >> 4), bd + (uint64_t)((k * 2048) >> 4),
+                       idesc, (pi > 0 || k > 0) ? 1u : 0u);
           tc_commit(b_empty(sb_i));
         }
-        if (ok) tc_commit(a_empty(sa_i));
       }
-      if (ok) tc_commit(acc_full);
+      if (ok && leader) tc_commit(a_empty(sa_i));
     }
+    if (ok && leader) tc_commit(acc_full);
   } else {
     const int q = warp & 3;
     const int ko = kt * BM + q * 32 + lane;

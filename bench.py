@@ -168,7 +168,7 @@ def side_configs(torch, fz, wl, handle, pk):
             pack[t] = fz.Buffer.importPointer(handle, tt.data_ptr(), tt.numel() * tt.element_size())
         return pack
 
-    def run(name, graph, ins, outs, tensors, work, unit, peak, bound, steps=10, flush=None):
+    def run(name, graph, ins, outs, tensors, work, unit, peak, bound, steps=10, flush=None, nbytes=None):
         graph.compile(handle)
         wsz = graph.getWorkspaceSize()
         wst = torch.empty(max(wsz, 1), dtype=torch.uint8, device="cuda")
@@ -189,6 +189,13 @@ def side_configs(torch, fz, wl, handle, pk):
         ach = work / t / (1e12 if unit == "TFLOP/s" else 1e9)
         out[name] = {"ms": t * 1e3, "achieved": ach, "unit": unit, "bound": bound, "peak": peak,
                      "frac": ach / peak, "launches": graph.numLaunches(), "workspace_bytes": wsz}
+        if nbytes is not None and unit == "TFLOP/s":
+            # two-sided roofline: the slower of the tensor-core time and the HBM time of the
+            # algorithmic bytes (each operand read once, the result written once)
+            t_tensor, t_hbm = work / (peak * 1e12), nbytes / (pk["hbm"] * 1e9)
+            out[name].update({"algorithmic_bytes": nbytes, "roofline_ms": max(t_tensor, t_hbm) * 1e3,
+                              "roofline_bound": "hbm" if t_hbm > t_tensor else "tensor",
+                              "frac_of_roofline": max(t_tensor, t_hbm) / t})
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     # C5: LayerNorm / RMSNorm / row sum on X[32768, 8192] bf16
@@ -242,11 +249,15 @@ def side_configs(torch, fz, wl, handle, pk):
             fl = 2.0 * n * hw * hw * c * kk * r * r
             tag = f"C4_{hw}x{hw}_c{c}_k{kk}_{r}x{r}"
             g, ins, o = wl.conv_fprop_bias_relu(n, c, hw, hw, kk, r, r, pad, DataType.BFloat16, bias=False, relu=False)
-            run(tag + "_fprop", g, ins, [(o, yy)], {"x": xx, "w": ww}, fl, "TFLOP/s", pk["tf_burst"], "tensor", steps=5, flush=flush)
+            nb = lambda *ts: float(sum(t.numel() * t.element_size() for t in ts))
+            run(tag + "_fprop", g, ins, [(o, yy)], {"x": xx, "w": ww}, fl, "TFLOP/s", pk["tf_burst"], "tensor", steps=5, flush=flush,
+                nbytes=nb(xx, ww, yy))
             g, ins, o = wl.conv_dgrad(n, c, hw, hw, kk, r, r, pad)
-            run(tag + "_dgrad", g, ins, [(o, dx)], {"dy": dy, "w": ww}, fl, "TFLOP/s", pk["tf_burst"], "tensor", steps=5, flush=flush)
+            run(tag + "_dgrad", g, ins, [(o, dx)], {"dy": dy, "w": ww}, fl, "TFLOP/s", pk["tf_burst"], "tensor", steps=5, flush=flush,
+                nbytes=nb(dy, ww, dx))
             g, ins, o = wl.conv_wgrad(n, c, hw, hw, kk, r, r, pad)
-            run(tag + "_wgrad", g, ins, [(o, dw)], {"dy": dy, "x": xx}, fl, "TFLOP/s", pk["tf_burst"], "tensor", steps=5, flush=flush)
+            run(tag + "_wgrad", g, ins, [(o, dw)], {"dy": dy, "x": xx}, fl, "TFLOP/s", pk["tf_burst"], "tensor", steps=5, flush=flush,
+                nbytes=nb(dy, xx, dw))
             del xx, ww, dy, yy, dx, dw
         except Exception as e:
             out[f"C4_{hw}x{hw}_c{c}_k{kk}_{r}x{r}"] = {"error": str(e)[:200]}

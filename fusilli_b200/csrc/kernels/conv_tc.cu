@@ -26,10 +26,14 @@ using namespace sm100;
 
 namespace {
 
-constexpr int BM = 128, BK = 64, STAGES = 4, MAX_BN = 256;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES_MAX = MAX_BN * BK * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES_MAX;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int BM = 128, BK = 64, MAX_BN = 256;
+constexpr int A_BYTES = BM * BK * 2;
+// The ring takes all of shared memory: a stage is the patch tile plus BN filter rows, so narrow
+// layers (BN = 64) get 9 stages, BN = 128 gets 7 and BN = 256 gets 4. What bounds these kernels on narrow
+// layers is bytes in flight per SM against L2 latency, not bandwidth.
+constexpr int MAX_STAGES = 12;
+constexpr int RING_BYTES = 229376; // 9 x 24 KB, 7 x 32 KB or 4 x 48 KB fit
+constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 
@@ -45,6 +49,7 @@ struct ConvTcParams {
   int32_t BN;                            // 64, 128 or 256
   int32_t cblocks;                       // ceil(Cred / 64)
   uint32_t a_bytes, b_bytes;
+  int32_t stages, stage_bytes;           // ring depth and bytes per stage (patch tile + BN filter rows)
   void *out;
   int64_t out_sn, out_sh, out_sw;        // element strides of the output (channel stride 1)
   uint32_t *err;
@@ -56,12 +61,14 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  const int STAGES = p.stages;
+  const uint32_t STAGE_BYTES = (uint32_t)p.stage_bytes;
+  const uint32_t bar_base = smem_base + RING_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t tmem_slot = bar_base + 8u * (2 * STAGES + 4);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * MAX_STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * MAX_STAGES + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -91,24 +98,25 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        // pixel tiles fastest so that concurrently running CTAs share the filter slice in L2
-        const int tp = tile % tiles_pix, tno = tile / tiles_pix;
-        const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
-        const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn, no0 = tno * p.BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+    // Whole warp in the loop, one elected lane issues: coordinates and addresses stay in uniform
+    // registers, and the channel-block / tap counters advance without divisions.
+    const bool leader = elect_one();
+    int s = 0;       // ring slot and its phase, advanced together (the depth is a run-time value)
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      // pixel tiles fastest so that concurrently running CTAs share the filter slice in L2
+      const int tp = tile % tiles_pix, tno = tile / tiles_pix;
+      const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
+      const int w0 = tw * p.bw + p.off_w, h0 = th * p.bh + p.off_h, n0 = tb * p.bn, no0 = tno * p.BN;
+      int cb = 0, ts = 0, tr = 0; // channel block (fastest), filter column, filter row
+      for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+        if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + A_BYTES;
+        const int c0 = cb * BK;
+        if (leader) {
           mbar_expect_tx(full_bar(s), p.a_bytes + p.b_bytes);
-          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-          const int cb = kb % p.cblocks, tap = kb / p.cblocks;
-          const int ts = tap % p.S, tr = tap / p.S;
-          const int c0 = cb * BK;
-          tma_load_4d(sa, &tmap_a, full_bar(s), c0, w0 + p.off_w + ts * p.step_w, h0 + p.off_h + tr * p.step_h, n0);
+          tma_load_4d(sa, &tmap_a, full_bar(s), c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
           if (!p.dgrad) {
             // filter rows ko, contraction channel c contiguous: one K-major box
             tma_load_4d(sb, &tmap_b, full_bar(s), c0, ts, tr, no0);
@@ -116,6 +124,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // filter rows ko (contraction), output channel c contiguous: MN-major 64-wide blocks
             for (int i = 0; i < p.BN / 64; ++i)
               tma_load_4d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), no0 + 64 * i, ts, tr, c0);
+          }
+        }
+        if (++cb == p.cblocks) {
+          cb = 0;
+          if (++ts == p.S) {
+            ts = 0;
+            ++tr;
           }
         }
       }
@@ -128,7 +143,8 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t b_lbo = p.dgrad ? 64 * BK * 2 : 16, b_kstep = p.dgrad ? 2048 : 32;
     const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
     const uint64_t b_desc0 = make_smem_desc(smem_base + A_BYTES, b_lbo, 1024);
-    uint32_t it = 0, lt = 0;
+    uint32_t lt = 0, ph = 0;
+    int s = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
       const int acc = lt & 1;
@@ -136,12 +152,10 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * MAX_BN;
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+      for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if (!mbar_wait(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t soff = (uint64_t)((s * STAGE_BYTES) >> 4);
+        const uint64_t soff = (uint64_t)(((uint32_t)s * STAGE_BYTES) >> 4);
         if (leader) {
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
@@ -350,6 +364,8 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
   p.total_tiles = (int)total;
   p.a_bytes = (uint32_t)p.rows * BK * 2;
   p.b_bytes = (uint32_t)p.BN * BK * 2;
+  p.stage_bytes = A_BYTES + p.BN * BK * 2;
+  p.stages = std::min(MAX_STAGES, RING_BYTES / p.stage_bytes);
   p.out = optr;
   p.err = cx.dev->error_word;
   p.epi.num_ops = s.num_epilogue;

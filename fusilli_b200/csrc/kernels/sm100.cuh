@@ -68,6 +68,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   return false;
 }
 
+// The same wait for a whole converged warp that stays in uniform control flow: one elected lane
+// polls (32 lanes polling one mbarrier are 32 shared-memory transactions per try), a vote
+// spreads the answer.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, uint32_t *err, uint32_t code) {
+  for (uint32_t it = 0; it < kWaitSpins; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "setp.eq.u32 p, 0, 1;\n\t"
+        "@q mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (__any_sync(0xffffffffu, ok != 0)) return true;
+    if (it > 2048) __nanosleep(128);
+  }
+  if (err && (threadIdx.x & 31) == 0) atomicOr(err, code);
+  return false;
+}
+
 // 3-D tiled TMA load into this CTA's shared memory, completion on `bar`.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
   asm volatile(
@@ -127,6 +149,26 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same MMA and commit for a whole converged warp in uniform control flow: the instruction is
+// predicated on an in-line election (always the same lane for a full mask), so the C++ around it
+// has no divergent region and the compiler keeps descriptors and addresses in uniform registers.
+__device__ __forceinline__ void tc_mma_f16_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(bar)
       : "memory");
 }
 // A from TMEM (16-bit values packed two per 32-bit column), B from shared memory.

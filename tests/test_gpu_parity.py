@@ -46,6 +46,26 @@ def test_conv_resnet_layers_bf16_fprop_dgrad_wgrad(shape):
     check_graph(g, _inputs(ins, 3, per={"dy": dy_dist, "x": x_dist}), scale_atol=0.05)
 
 
+@pytest.mark.parametrize("shape", [
+    (2, 96, 30, 24, 160, 3, 3, 1),   # ragged channel block and ragged output-channel tile
+    (1, 64, 32, 32, 64, 5, 5, 2),    # 5x5 taps, resident filter
+    (1, 64, 34, 34, 128, 3, 3, 0),   # no padding: output 32x32
+    (1, 64, 16, 16, 512, 3, 3, 1),   # two output-channel tiles, streamed filter
+    (3, 128, 56, 56, 64, 3, 3, 1),   # several patch slots in flight per tile
+])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_conv_halo_tiles(shape, dtype):
+    """3x3 / 5x5 unit-stride layers large enough for the kernel that loads one haloed patch per
+    channel block and reads every tap as a shifted window of it; fprop with fused bias + ReLU and
+    dgrad."""
+    n, c, h, w, k, r, s, pad = shape
+    x_dist, dy_dist = ("normal", 0.0, 0.05), ("normal", 0.0, 0.01)
+    g, ins, _ = wl.conv_fprop_bias_relu(n, c, h, w, k, r, s, pad, dtype)
+    check_graph(g, _inputs(ins, 4, x_dist, per={"bias": ("uniform", -0.1, 0.1)}))
+    g, ins, _ = wl.conv_dgrad(n, c, h, w, k, r, s, pad, dtype)
+    check_graph(g, _inputs(ins, 5, per={"dy": dy_dist, "w": x_dist}), scale_atol=0.05)
+
+
 @pytest.mark.parametrize("dtype", [F16, F32])
 @pytest.mark.parametrize("case", ["grouped_strided", "nchw", "dilated", "conv1d", "conv3d"])
 def test_conv_variants(dtype, case):

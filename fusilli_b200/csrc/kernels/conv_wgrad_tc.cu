@@ -88,62 +88,76 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t ia = 0, ib = 0;
-      bool ok = true;
-      for (int pi = 0; pi < npatch && ok; ++pi, ++ia) {
-        const int patch = patch0 + pi;
-        const int tw = patch % p.tiles_w, th = (patch / p.tiles_w) % p.tiles_h, tb = patch / (p.tiles_w * p.tiles_h);
-        const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn;
-        const int sa_i = ia % A_STAGES;
-        if (!mbar_wait(a_empty(sa_i), ((ia / A_STAGES) & 1) ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        mbar_expect_tx(a_full(sa_i), a_bytes);
-        const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
-        for (int hh = 0; hh < p.a_halves; ++hh)
-          tma_load_4d(sa + hh * HALF, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
-        for (int t = 0; t < ntaps; ++t, ++ib) {
-          const int tap = tap0 + t, ts = tap % p.S, tr = tap / p.S;
-          const int sb_i = ib % B_STAGES;
-          if (!mbar_wait(b_empty(sb_i), ((ib / B_STAGES) & 1) ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-          mbar_expect_tx(b_full(sb_i), b_bytes);
-          const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
-          for (int i = 0; i < p.BN / 64; ++i)
-            tma_load_4d(sb + i * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i, w0 - p.pad_w + ts * p.dil_w,
-                        h0 - p.pad_h + tr * p.dil_h, n0);
+    // Whole warp in the loop, every issue predicated on an in-line election: coordinates stay in
+    // uniform registers and the tap counters advance without divisions.
+    int sa_i = 0, sb_i = 0;
+    uint32_t pha = 0, phb = 0;
+    bool ok = true;
+    const int ts0 = tap0 % p.S, tr0 = tap0 / p.S;
+    int tw = patch0 % p.tiles_w, th = (patch0 / p.tiles_w) % p.tiles_h, tb = patch0 / (p.tiles_w * p.tiles_h);
+    for (int pi = 0; pi < npatch && ok; ++pi) {
+      const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn;
+      if (!mbar_wait_warp(a_empty(sa_i), pha ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+      mbar_expect_tx_elect(a_full(sa_i), a_bytes);
+      const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
+      for (int hh = 0; hh < p.a_halves; ++hh)
+        tma_load_4d_elect(sa + hh * HALF, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
+      sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
+      pha ^= (sa_i == 0);
+      int ts = ts0, tr = tr0;
+      for (int t = 0; t < ntaps; ++t) {
+        if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        mbar_expect_tx_elect(b_full(sb_i), b_bytes);
+        const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
+        for (int i = 0; i < p.BN / 64; ++i)
+          tma_load_4d_elect(sb + i * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i, w0 - p.pad_w + ts * p.dil_w,
+                            h0 - p.pad_h + tr * p.dil_h, n0);
+        sb_i = (sb_i + 1 == B_STAGES) ? 0 : sb_i + 1;
+        phb ^= (sb_i == 0);
+        if (++ts == p.S) {
+          ts = 0;
+          ++tr;
+        }
+      }
+      if (++tw == p.tiles_w) {
+        tw = 0;
+        if (++th == p.tiles_h) {
+          th = 0;
+          ++tb;
         }
       }
     }
   } else if (warp == 1) {
     // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
     // elected lane issues the MMAs and the commits, which track the issuing thread.
-    const bool leader = elect_one();
     const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 1, 1);
     // both tiles MN-major: 64-channel blocks HALF apart (LBO), 8-pixel groups 1024 B apart,
     // a 16-pixel K step is 2048 B
     const uint64_t a_desc0 = make_smem_desc(smem_base, HALF, 1024);
     const uint64_t b_desc0 = make_smem_desc(sb_base, HALF, 1024);
-    uint32_t ia = 0, ib = 0;
+    int sa_i = 0, sb_i = 0;
+    uint32_t pha = 0, phb = 0;
     bool ok = true;
-    for (int pi = 0; pi < npatch && ok; ++pi, ++ia) {
-      const int sa_i = ia % A_STAGES;
-      if (!mbar_wait(a_full(sa_i), (ia / A_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+    for (int pi = 0; pi < npatch && ok; ++pi) {
+      if (!mbar_wait_warp(a_full(sa_i), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
       const uint64_t ad = a_desc0 + (uint64_t)((sa_i * A_STAGE_BYTES) >> 4);
-      for (int t = 0; t < ntaps; ++t, ++ib) {
-        const int sb_i = ib % B_STAGES;
-        if (!mbar_wait(b_full(sb_i), (ib / B_STAGES) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+      for (int t = 0; t < ntaps; ++t) {
+        if (!mbar_wait_warp(b_full(sb_i), phb, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint64_t bd = b_desc0 + (uint64_t)((sb_i * B_STAGE_BYTES) >> 4);
-        if (leader) {
 #pragma unroll
-          for (int k = 0; k < KPIX / 16; ++k)
-            tc_mma_f16(tmem_base + t * p.BN, ad + (uint64_t)((k * 2048) >> 4), bd + (uint64_t)((k * 2048) >> 4),
-                       idesc, (pi > 0 || k > 0) ? 1u : 0u);
-          tc_commit(b_empty(sb_i));
-        }
+        for (int k = 0; k < KPIX / 16; ++k)
+          tc_mma_f16_elect(tmem_base + t * p.BN, ad + (uint64_t)((k * 2048) >> 4), bd + (uint64_t)((k * 2048) >> 4),
+                           idesc, (pi > 0 || k > 0) ? 1u : 0u);
+        tc_commit_elect(b_empty(sb_i));
+        sb_i = (sb_i + 1 == B_STAGES) ? 0 : sb_i + 1;
+        phb ^= (sb_i == 0);
       }
-      if (ok && leader) tc_commit(a_empty(sa_i));
+      if (ok) tc_commit_elect(a_empty(sa_i));
+      sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
+      pha ^= (sa_i == 0);
     }
-    if (ok && leader) tc_commit(acc_full);
+    if (ok) tc_commit_elect(acc_full);
   } else {
     const int q = warp & 3;
     const int ko = kt * BM + q * 32 + lane;

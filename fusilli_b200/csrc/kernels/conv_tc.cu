@@ -168,17 +168,15 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
         const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + A_BYTES;
         const int c0 = cb * BK;
-        if (leader) {
-          mbar_expect_tx(full_bar(s), p.a_bytes + p.b_bytes);
-          tma_load_4d(sa, &tmap_a, full_bar(s), c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
-          if (!p.dgrad) {
-            // filter rows ko, contraction channel c contiguous: one K-major box
-            tma_load_4d(sb, &tmap_b, full_bar(s), c0, ts, tr, no0);
-          } else {
-            // filter rows ko (contraction), output channel c contiguous: MN-major 64-wide blocks
-            for (int i = 0; i < p.BN / 64; ++i)
-              tma_load_4d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), no0 + 64 * i, ts, tr, c0);
-          }
+        mbar_expect_tx_elect(full_bar(s), p.a_bytes + p.b_bytes);
+        tma_load_4d_elect(sa, &tmap_a, full_bar(s), c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
+        if (!p.dgrad) {
+          // filter rows ko, contraction channel c contiguous: one K-major box
+          tma_load_4d_elect(sb, &tmap_b, full_bar(s), c0, ts, tr, no0);
+        } else {
+          // filter rows ko (contraction), output channel c contiguous: MN-major 64-wide blocks
+          for (int i = 0; i < p.BN / 64; ++i)
+            tma_load_4d_elect(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), no0 + 64 * i, ts, tr, c0);
         }
         if (++cb == p.cblocks) {
           cb = 0;
@@ -210,15 +208,13 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (!mbar_wait_warp(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint64_t soff = (uint64_t)(((uint32_t)s * STAGE_BYTES) >> 4);
-        if (leader) {
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            tc_mma_f16(d_tmem, a_desc0 + soff + (uint64_t)((k * 32) >> 4),
-                       b_desc0 + soff + (uint64_t)((k * b_kstep) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          tc_commit(empty_bar(s));
-        }
+        for (int k = 0; k < BK / 16; ++k)
+          tc_mma_f16_elect(d_tmem, a_desc0 + soff + (uint64_t)((k * 32) >> 4),
+                           b_desc0 + soff + (uint64_t)((k * b_kstep) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        tc_commit_elect(empty_bar(s));
       }
-      if (ok && leader) tc_commit(tfull_bar(acc));
+      if (ok) tc_commit_elect(tfull_bar(acc));
     }
   } else {
     conv_epilogue_warps(p, tmem_base, tfull_bar(0), tempty_bar(0), warp, lane);

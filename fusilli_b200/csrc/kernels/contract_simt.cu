@@ -258,6 +258,90 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(const ContractParams
   }
 }
 
+// Channels-last fp32 forward convolution (2-D, channel count a multiple of 16): the same implicit
+// GEMM as above with the index arithmetic hoisted out of the loop. A 16-wide reduction tile is 16
+// consecutive channels of ONE filter tap, so per tile a thread does one bounds test and one
+// 16-byte load per pixel row instead of a full coordinate decomposition per element. Tile 128
+// pixels x 64 output channels x 16, 8 x 4 outputs per thread, next tile prefetched in registers.
+constexpr int FBM = 128, FBN = 64, FBK = 16;
+__global__ void __launch_bounds__(256) conv_fprop_cl_f32_kernel(const ContractParams p) {
+  __shared__ __align__(16) float As[FBK][FBM + 4];
+  __shared__ __align__(16) float Bs[FBK][FBN + 4];
+  const ConvGeomDev &q = p.g;
+  const int tid = threadIdx.x;
+  const int g = blockIdx.z;
+  const int m0 = blockIdx.x * FBM, n0 = blockIdx.y * FBN;
+  const float *x = static_cast<const float *>(p.a), *wt = static_cast<const float *>(p.b);
+  // staging: two pixel rows and one filter row per thread, four consecutive channels each
+  const int k4 = (tid & 3) * 4;
+  int64_t a_base[2];
+  int a_ih0[2], a_iw0[2];
+  bool a_ok[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + (tid >> 2) + 64 * i;
+    a_ok[i] = m < p.M;
+    int n, od, oh, ow;
+    split_pos(a_ok[i] ? m : 0, q.OD, q.OH, q.OW, n, od, oh, ow);
+    a_base[i] = (int64_t)n * q.xs[0] + (int64_t)g * q.Cg;
+    a_ih0[i] = oh * q.sh - q.ph;
+    a_iw0[i] = ow * q.sw - q.pw;
+  }
+  const int b_n = n0 + (tid >> 2);
+  const bool b_ok = b_n < p.N;
+  const int64_t b_base = (int64_t)(g * q.Kg + (b_ok ? b_n : 0)) * q.ws[0];
+  const int tx = tid & 15, ty = tid >> 4; // outputs: rows ty*8 .. +7, columns tx*4 .. +3
+  float acc[8][4] = {};
+  float4 ra[2], rb;
+  auto fetch_tile = [&](int k0) {
+    const int tap = k0 / q.Cg, c0 = k0 - tap * q.Cg + k4;
+    const int r = tap / q.S, ss = tap - r * q.S;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int ih = a_ih0[i] + r * q.dh, iw = a_iw0[i] + ss * q.dw;
+      const bool in = a_ok[i] && ih >= 0 && ih < q.H && iw >= 0 && iw < q.W;
+      ra[i] = in ? __ldg(reinterpret_cast<const float4 *>(x + a_base[i] + (int64_t)ih * q.xs[3] + (int64_t)iw * q.xs[4] + c0))
+                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    rb = b_ok ? __ldg(reinterpret_cast<const float4 *>(wt + b_base + (int64_t)r * q.ws[3] + (int64_t)ss * q.ws[4] + c0))
+              : make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  const int K = (int)p.K;
+  fetch_tile(0);
+  for (int k0 = 0; k0 < K; k0 += FBK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int m = (tid >> 2) + 64 * i;
+      As[k4 + 0][m] = ra[i].x; As[k4 + 1][m] = ra[i].y; As[k4 + 2][m] = ra[i].z; As[k4 + 3][m] = ra[i].w;
+    }
+    Bs[k4 + 0][tid >> 2] = rb.x; Bs[k4 + 1][tid >> 2] = rb.y; Bs[k4 + 2][tid >> 2] = rb.z; Bs[k4 + 3][tid >> 2] = rb.w;
+    __syncthreads();
+    if (k0 + FBK < K) fetch_tile(k0 + FBK);
+#pragma unroll
+    for (int kk = 0; kk < FBK; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4 *>(&As[kk][ty * 8]);
+      const float4 a1 = *reinterpret_cast<const float4 *>(&As[kk][ty * 8 + 4]);
+      const float4 bv = *reinterpret_cast<const float4 *>(&Bs[kk][tx * 4]);
+      const float a8[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, b4[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a8[i], b4[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int m = m0 + ty * 8 + i;
+    if (m >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int nn = n0 + tx * 4 + j;
+      if (nn < p.N) store_out(p, g, m, nn, acc[i][j]);
+    }
+  }
+}
+
 // Sums the split-K partial tiles in split order, then epilogue + store.
 __global__ void __launch_bounds__(256) contract_splitk_reduce_kernel(const ContractParams p) {
   int64_t total = (int64_t)p.G * p.M * p.N;
@@ -395,6 +479,17 @@ fb_status launch_contract_simt(const ExecContext &cx, const Step &s) {
   if (grid.y > 65535 || grid.z > 65535)
     return fail(FB_NOT_IMPLEMENTED, "contract: problem too large for the CUDA-core kernel's grid");
   cudaStream_t stream = cx.dev->stream;
+  if (p.mode == CM_FPROP && p.g.chan_fastest && p.a_dtype == FB_DT_FLOAT && p.b_dtype == FB_DT_FLOAT &&
+      p.g.nsp == 2 && p.g.Cg % FBK == 0 && p.g.xs[1] == 1 && p.g.ws[1] == 1 &&
+      (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.b) & 15) == 0 &&
+      p.g.xs[0] % 4 == 0 && p.g.xs[3] % 4 == 0 && p.g.xs[4] % 4 == 0 && p.g.ws[0] % 4 == 0 && p.g.ws[3] % 4 == 0 &&
+      p.g.ws[4] % 4 == 0) {
+    dim3 fgrid((unsigned)((p.M + FBM - 1) / FBM), (unsigned)((p.N + FBN - 1) / FBN), (unsigned)p.G);
+    if (fgrid.y <= 65535 && fgrid.z <= 65535) {
+      conv_fprop_cl_f32_kernel<<<fgrid, 256, 0, stream>>>(p);
+      return FB_OK;
+    }
+  }
   contract_simt_kernel<<<grid, 256, 0, stream>>>(p);
   if (p.split_k > 1) {
     int64_t total = (int64_t)p.G * p.M * p.N;

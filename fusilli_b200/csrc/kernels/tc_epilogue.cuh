@@ -30,13 +30,23 @@ struct TcEpilogue {
 
 #if defined(__CUDACC__)
 
+// Rounds 32 values to a 16-bit type and back, two per conversion instruction.
 __device__ __forceinline__ void epi_round_vec(float (&v)[32], int dt) {
   if (dt == FB_DT_BFLOAT16) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+    for (int j = 0; j < 16; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      const uint32_t w = *reinterpret_cast<uint32_t *>(&h);
+      v[2 * j] = __uint_as_float(w << 16);
+      v[2 * j + 1] = __uint_as_float(w & 0xffff0000u);
+    }
   } else if (dt == FB_DT_HALF) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __half2float(__float2half_rn(v[j]));
+    for (int j = 0; j < 16; ++j) {
+      const float2 f = __half22float2(__floats2half2_rn(v[2 * j], v[2 * j + 1]));
+      v[2 * j] = f.x;
+      v[2 * j + 1] = f.y;
+    }
   }
 }
 
@@ -127,7 +137,9 @@ __device__ __forceinline__ void epi_apply_vec(const TcEpiOp &op, float (&v)[32],
 // Full epilogue for 32 columns [nc, nc+32) of one output row; `row_off` is the element
 // offset of the row start in the output (and in same-layout operands).
 __device__ __forceinline__ void epi_run32(const TcEpilogue &e, float (&v)[32], int64_t row_off, int nc, int valid) {
-  epi_round_vec(v, e.acc_round_dtype);
+  // Every stage rounds to its declared dtype, except a last stage whose dtype is the stored one:
+  // the store performs that very rounding (rounding twice to one type changes nothing).
+  if (!(e.num_ops == 0 && e.acc_round_dtype == e.out_dtype)) epi_round_vec(v, e.acc_round_dtype);
 #pragma unroll 1
   for (int i = 0; i < e.num_ops; ++i) {
     const TcEpiOp &op = e.ops[i];
@@ -139,7 +151,7 @@ __device__ __forceinline__ void epi_run32(const TcEpilogue &e, float (&v)[32], i
       for (int j = 0; j < 32; ++j) o[j] = op.scalar;
     }
     epi_apply_vec(op, v, o);
-    epi_round_vec(v, op.round_dtype);
+    if (!(i == e.num_ops - 1 && op.round_dtype == e.out_dtype)) epi_round_vec(v, op.round_dtype);
   }
 }
 

@@ -108,6 +108,27 @@ def test_conv_variants(dtype, case):
         check_graph(g2, _inputs(ins, 8), scale_atol=8.0 if dtype == F32 else 2.0)
 
 
+@pytest.mark.parametrize("geom", [
+    # x dims (NCHW logical), w dims, pad, stride, dilation
+    ([3, 32, 19, 23], [24, 32, 3, 3], [1, 1], [1, 1], [1, 1]),   # ragged pixel and output-channel tiles
+    ([2, 48, 17, 17], [40, 48, 3, 3], [2, 2], [2, 2], [2, 2]),   # stride and dilation
+    ([2, 64, 12, 12], [32, 16, 3, 3], [1, 1], [1, 1], [1, 1]),   # four groups of 16 channels
+    ([1, 16, 9, 30], [16, 16, 1, 5], [0, 2], [1, 1], [1, 1]),    # 1x5 taps
+])
+def test_conv_fprop_f32_channels_last(geom):
+    """fp32 channels-last forward convolutions whose channel count per group is a multiple of 16: the
+    CUDA-core kernel with the hoisted index arithmetic; results to the fp32 tolerance."""
+    xd, wd, pad, st, dl = geom
+    g = fz.Graph()
+    g.setName("conv_f32_cl").setIODataType(F32).setComputeDataType(F32).setIntermediateDataType(F32)
+    x = g.tensor(TensorAttr().setName("x").setDim(xd).setStride(channelsLastStride(xd)))
+    w = g.tensor(TensorAttr().setName("w").setDim(wd).setStride(channelsLastStride(wd)))
+    y = g.convFProp(x, w, fz.ConvFPropAttr().setPadding(pad).setStride(st).setDilation(dl))
+    y.setName("y").setOutput(True)
+    g.validate()
+    check_graph(g, _inputs({"x": x, "w": w}, 9), scale_atol=4.0)
+
+
 # ---- matmul -------------------------------------------------------------------------
 @pytest.mark.parametrize("cfg", [
     # b, m, n, k, dtype, bias, trans_b

@@ -34,7 +34,7 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 12;
 constexpr int RING_BYTES = 229376; // 9 x 24 KB, 7 x 32 KB or 4 x 48 KB fit
 constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 constexpr int TMEM_COLS = 512;
 
 struct ConvTcParams {
@@ -63,9 +63,11 @@ struct ConvTcParams {
   TcEpilogue epi;
 };
 
-// Epilogue warps (2..5) of both convolution kernels: accumulator tile -> registers -> fused
-// pointwise chain -> global memory, one output pixel (row) per thread. tfull0 / tempty0 are the
-// barriers of accumulator 0; accumulator 1's follow 8 bytes later.
+// Epilogue warps (2..9) of both convolution kernels: accumulator tile -> registers -> fused
+// pointwise chain -> global memory, one output pixel (row) per thread. Two warps share a TMEM lane
+// quarter (warp index mod 4) and split the tile's columns in halves: on layers with few channel
+// blocks per tile the epilogue, not the MMAs, sets the pace. tfull0 / tempty0 are the barriers of
+// accumulator 0; accumulator 1's follow 8 bytes later.
 __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint32_t tmem_base, uint32_t tfull0,
                                                     uint32_t tempty0, int warp, int lane) {
   const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
@@ -87,12 +89,13 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint3
     const int no0 = tno * p.BN;
     const uint32_t taddr = tmem_base + acc * MAX_BN + ((uint32_t)(q * 32) << 16);
     const int nchunks = p.BN / 32;
+    const int c_begin = ((warp - 2) >> 2) * (nchunks / 2), c_end = c_begin + nchunks / 2;
 #pragma unroll 1
-    for (int c = 0; c < nchunks; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
       uint32_t raw[32];
       tmem_ld_32x32(taddr + c * 32, raw);
       tmem_ld_wait();
-      if (c == nchunks - 1) {
+      if (c == c_end - 1) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
@@ -132,7 +135,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 4);
+      mbar_init(tempty_bar(a), 8);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -268,7 +271,7 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8u * a, 1);
-      mbar_init(tempty0 + 8u * a, 4);
+      mbar_init(tempty0 + 8u * a, 8);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);

@@ -78,7 +78,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, ui
         "{\n\t.reg .pred p, q;\n\t"
         "elect.sync _|q, 0xffffffff;\n\t"
         "setp.eq.u32 p, 0, 1;\n\t"
-        "@q mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@q mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)

@@ -7,7 +7,8 @@ reference's samples include), linked to fusilli_b200/libfusilli_b200.so:
   own_*   tests/cpp/*.cpp of this repository;
   ref_*   the reference project's sample and unit-test sources for the operators this backend
           implements, compiled UNCHANGED from the reference checkout (directory given by
-          FUSILLI_REFERENCE_DIR, default /root/reference) when that checkout is present. Nothing
+          FUSILLI_REFERENCE_DIR, default: a `reference/` directory beside this repository) when that
+          checkout is present. Nothing
           is copied: only the built programs land in tests/cpp/_build/.
 
 Run as `python tests/cpp/build.py [-j N] [--only PATTERN]`.
@@ -22,7 +23,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 OUT = os.path.join(HERE, "_build")
-REFERENCE = os.environ.get("FUSILLI_REFERENCE_DIR", "/root/reference")
+REFERENCE = os.environ.get("FUSILLI_REFERENCE_DIR", os.path.normpath(os.path.join(ROOT, "..", "reference")))
 CXX = os.environ.get("FUSILLI_TEST_CXX", "/usr/bin/g++")
 
 OWN_SOURCES = ["test_frontend_host.cpp", "test_frontend_device.cpp"]

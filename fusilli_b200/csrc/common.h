@@ -71,6 +71,7 @@ struct TensorInfo {
   int64_t dims[FB_MAX_RANK] = {0};
   int64_t strides[FB_MAX_RANK] = {0};
   double scalar = 0.0;
+  uint32_t dynamic_mask = 0; // bit k: logical dim k takes its extent at execute
   int64_t ws_offset = -1; // >= 0: materialised in the workspace at this byte offset
   int64_t phys_elems() const; // elements of the dense physical buffer
 };
@@ -124,11 +125,20 @@ struct Plan {
   int32_t num_args = 0;
   size_t workspace_bytes = 0;
   std::vector<int32_t> arg_tensor; // arg index -> tensor id
+  bool has_dynamic_dims() const {
+    for (const TensorInfo &t : tensors)
+      if (t.dynamic_mask) return true;
+    return false;
+  }
 };
 
 // Lowers tensors+nodes (already filled in `plan`) to steps; FB_NOT_IMPLEMENTED
 // for graphs the kernels cannot run.
 fb_status lower(Plan &plan);
+// `base` with the dynamic dims of its bound tensors replaced by `arg_dims` (FB_MAX_RANK logical
+// extents per argument), the dims of virtual tensors derived from the nodes' shape rules, dense
+// strides regenerated, and the steps lowered again for the concrete shape.
+fb_status specialize(const Plan &base, const int64_t *arg_dims, Plan &out);
 fb_status serialize(const Plan &plan, std::vector<uint8_t> &out);
 fb_status deserialize(const uint8_t *bytes, size_t n, Plan &plan);
 std::string stats_json(const Plan &plan);

@@ -257,6 +257,185 @@ fb_status lower(Plan &p) {
   return FB_OK;
 }
 
+// ---- dynamic dims --------------------------------------------------------------
+// The reference marks dims as dynamic on the tensors (tensor_attributes.h:71-84): dims and strides
+// stay representative, the emitted function takes `?` extents, and the buffers of each call carry
+// the concrete ones. Here the plan keeps the whole graph, so a call with new extents re-derives
+// the shapes and lowers again.
+
+// Dense strides for `t.dims` in the layout order of the representative strides (innermost =
+// smallest stride; among equal strides, which only unit dims have, the later dim is inner).
+static void restride(TensorInfo &t) {
+  int order[FB_MAX_RANK];
+  for (int i = 0; i < t.rank; ++i) order[i] = i;
+  for (int i = 1; i < t.rank; ++i)
+    for (int j = i; j > 0; --j) {
+      const int a = order[j - 1], b = order[j];
+      const bool b_inner = t.strides[b] < t.strides[a] || (t.strides[b] == t.strides[a] && b > a);
+      if (!b_inner) break;
+      order[j - 1] = b;
+      order[j] = a;
+    }
+  int64_t run = 1;
+  for (int i = 0; i < t.rank; ++i) {
+    t.strides[order[i]] = run;
+    run *= t.dims[order[i]];
+  }
+}
+
+// Extent of dim `k` of output `slot` of node `d` as its inputs imply it, -1 when the node gives
+// no rule (the reference makes the user state dX and dW dims, conv_node.h:546-559).
+static int64_t implied_out_dim(const Plan &p, const fb_node_desc &d, int slot, int k) {
+  auto T = [&](int id) -> const TensorInfo & { return p.tensors[id]; };
+  switch (d.op) {
+  case FB_OP_CONV_FPROP: {
+    const TensorInfo &x = T(d.inputs[0]), &w = T(d.inputs[1]);
+    if (k == 0) return x.dims[0];
+    if (k == 1) return w.dims[0];
+    const int s = k - 2;
+    return 1 + (x.dims[k] + 2 * d.padding[s] - (w.dims[k] - 1) * d.dilation[s] - 1) / d.stride[s];
+  }
+  case FB_OP_CONV_DGRAD: return k == 0 ? T(d.inputs[0]).dims[0] : -1;
+  case FB_OP_CONV_WGRAD: return -1;
+  case FB_OP_MATMUL: {
+    const TensorInfo &a = T(d.inputs[0]), &b = T(d.inputs[1]);
+    const int r = T(d.outputs[0]).rank;
+    if (a.rank != r || b.rank != r) return -1;
+    if (k == r - 2) return a.dims[r - 2];
+    if (k == r - 1) return b.dims[r - 1];
+    return a.dims[k] > b.dims[k] ? a.dims[k] : b.dims[k];
+  }
+  case FB_OP_SDPA: return k == 3 ? T(d.inputs[2]).dims[3] : T(d.inputs[0]).dims[k];
+  case FB_OP_LAYERNORM:
+  case FB_OP_RMSNORM:
+    if (slot == 0 || k == 0) return T(d.inputs[0]).dims[k];
+    return 1;
+  case FB_OP_REDUCTION: return T(d.inputs[0]).dims[k]; // a dynamic dim is never a reduced one
+  case FB_OP_POINTWISE: {
+    const int r = T(d.outputs[0]).rank;
+    int64_t v = 1;
+    for (int i = 0; i < FB_MAX_NODE_INPUTS; ++i) {
+      if (d.inputs[i] < 0) continue;
+      const TensorInfo &in = T(d.inputs[i]);
+      const int idx = k - (r - in.rank);
+      if (idx >= 0 && in.dims[idx] > v) v = in.dims[idx];
+    }
+    return v;
+  }
+  default: return -1;
+  }
+}
+
+// What validate() checked on the representative shape and a new extent can break.
+static fb_status check_runtime_shapes(const Plan &p, const NodeInfo &n) {
+  const fb_node_desc &d = n.d;
+  auto T = [&](int id) -> const TensorInfo & { return p.tensors[id]; };
+  auto bad = [&](const std::string &what) {
+    return fail(FB_INVALID_ARGUMENT, "node '" + n.name + "': runtime shapes disagree: " + what);
+  };
+  switch (d.op) {
+  case FB_OP_CONV_FPROP:
+  case FB_OP_CONV_DGRAD:
+  case FB_OP_CONV_WGRAD: {
+    // (image, filter, result) in fprop roles: fprop X,W,Y; dgrad DX,W,DY; wgrad X,DW,DY
+    const TensorInfo &img = d.op == FB_OP_CONV_FPROP ? T(d.inputs[0]) : (d.op == FB_OP_CONV_DGRAD ? T(d.outputs[0]) : T(d.inputs[1]));
+    const TensorInfo &flt = d.op == FB_OP_CONV_WGRAD ? T(d.outputs[0]) : T(d.inputs[1]);
+    const TensorInfo &res = d.op == FB_OP_CONV_FPROP ? T(d.outputs[0]) : T(d.inputs[0]);
+    if (img.dims[0] != res.dims[0]) return bad("batch sizes differ");
+    for (int k = 2; k < img.rank; ++k) {
+      const int s = k - 2;
+      const int64_t want = 1 + (img.dims[k] + 2 * d.padding[s] - (flt.dims[k] - 1) * d.dilation[s] - 1) / d.stride[s];
+      if (want != res.dims[k]) return bad("spatial dim " + std::to_string(s) + " of the convolution result");
+    }
+    return FB_OK;
+  }
+  case FB_OP_MATMUL: {
+    const TensorInfo &a = T(d.inputs[0]), &b = T(d.inputs[1]);
+    if (a.dims[a.rank - 1] != b.dims[b.rank - 2]) return bad("matmul K");
+    for (int k = 0; k + 2 < a.rank && a.rank == b.rank; ++k)
+      if (a.dims[k] != b.dims[k] && a.dims[k] != 1 && b.dims[k] != 1 && a.dims[k] % b.dims[k] != 0 &&
+          b.dims[k] % a.dims[k] != 0)
+        return bad("matmul batch dims");
+    return FB_OK;
+  }
+  case FB_OP_SDPA: {
+    const TensorInfo &q = T(d.inputs[0]), &k = T(d.inputs[1]), &v = T(d.inputs[2]);
+    if (q.dims[0] != k.dims[0] || q.dims[0] != v.dims[0]) return bad("SDPA batch");
+    if (k.dims[2] != v.dims[2]) return bad("SDPA key and value sequence lengths");
+    if (q.dims[3] != k.dims[3]) return bad("SDPA head dim");
+    if (d.inputs[3] >= 0) {
+      const TensorInfo &m = T(d.inputs[3]);
+      const int64_t full[4] = {q.dims[0], q.dims[1], q.dims[2], k.dims[2]};
+      for (int i = 0; i < 4; ++i)
+        if (m.dims[i] != 1 && m.dims[i] != full[i]) return bad("SDPA mask");
+    }
+    return FB_OK;
+  }
+  case FB_OP_LAYERNORM:
+  case FB_OP_RMSNORM: {
+    const TensorInfo &x = T(d.inputs[0]);
+    const int nparams = d.op == FB_OP_LAYERNORM ? 2 : 1;
+    for (int i = 1; i <= nparams; ++i) {
+      if (d.inputs[i] < 0) continue;
+      const TensorInfo &g = T(d.inputs[i]);
+      for (int k = 1; k < x.rank && g.rank == x.rank; ++k)
+        if (g.dims[k] != x.dims[k]) return bad("normalisation scale / bias");
+    }
+    return FB_OK;
+  }
+  default: return FB_OK; // pointwise broadcasting is re-checked by the lowering
+  }
+}
+
+fb_status specialize(const Plan &base, const int64_t *arg_dims, Plan &out) {
+  FB_REQUIRE(arg_dims != nullptr, FB_INVALID_ARGUMENT, "runtime dims are NULL");
+  out = base;
+  out.steps.clear();
+  for (TensorInfo &t : out.tensors) t.ws_offset = -1;
+  for (int a = 0; a < out.num_args; ++a) {
+    TensorInfo &t = out.tensors[out.arg_tensor[a]];
+    const int64_t *rt = arg_dims + (size_t)a * FB_MAX_RANK;
+    for (int k = 0; k < t.rank; ++k) {
+      FB_REQUIRE(rt[k] >= 1, FB_INVALID_ARGUMENT,
+                 "tensor '" + t.name + "': runtime dim " + std::to_string(k) + " is " + std::to_string(rt[k]));
+      if (t.dynamic_mask >> k & 1) continue;
+      FB_REQUIRE(rt[k] == t.dims[k], FB_INVALID_ARGUMENT,
+                 "tensor '" + t.name + "': dim " + std::to_string(k) + " is static (" + std::to_string(t.dims[k]) +
+                     ") but the buffer has " + std::to_string(rt[k]));
+    }
+    if (t.dynamic_mask) {
+      for (int k = 0; k < t.rank; ++k) t.dims[k] = rt[k];
+      restride(t);
+    }
+  }
+  for (const NodeInfo &n : out.nodes) {
+    for (int slot = 0; slot < FB_MAX_NODE_OUTPUTS; ++slot) {
+      const int id = n.d.outputs[slot];
+      if (id < 0 || out.tensors[id].dynamic_mask == 0) continue;
+      TensorInfo &t = out.tensors[id];
+      for (int k = 0; k < t.rank; ++k) {
+        if (!(t.dynamic_mask >> k & 1)) continue;
+        const int64_t v = implied_out_dim(out, n.d, slot, k);
+        if (t.role == FB_TENSOR_VIRTUAL) {
+          FB_REQUIRE(v >= 1, FB_NOT_IMPLEMENTED,
+                     "node '" + n.name + "': dynamic dim " + std::to_string(k) + " of virtual tensor '" + t.name +
+                         "' does not follow from the node's inputs");
+          t.dims[k] = v;
+        } else {
+          FB_REQUIRE(v < 0 || v == t.dims[k], FB_INVALID_ARGUMENT,
+                     "tensor '" + t.name + "': the buffer's dim " + std::to_string(k) + " is " +
+                         std::to_string(t.dims[k]) + " but the inputs of node '" + n.name + "' imply " +
+                         std::to_string(v));
+        }
+      }
+      if (t.role == FB_TENSOR_VIRTUAL) restride(t);
+    }
+    fb_status st = check_runtime_shapes(out, n);
+    if (st != FB_OK) return st;
+  }
+  return lower(out);
+}
+
 // ---- serialisation -----------------------------------------------------------
 // Layout: magic[8] | abi u32 | arch u32 | payload_len u64 | fnv1a64(payload) u64 | payload
 
@@ -320,6 +499,7 @@ fb_status serialize(const Plan &p, std::vector<uint8_t> &out) {
     for (int i = 0; i < FB_MAX_RANK; ++i) w.pod(t.dims[i]);
     for (int i = 0; i < FB_MAX_RANK; ++i) w.pod(t.strides[i]);
     w.pod(t.scalar);
+    w.pod(t.dynamic_mask);
     w.pod(t.ws_offset);
   }
   w.pod<uint32_t>((uint32_t)p.nodes.size());
@@ -370,6 +550,7 @@ fb_status deserialize(const uint8_t *bytes, size_t n, Plan &p) {
     for (int i = 0; i < FB_MAX_RANK; ++i) t.dims[i] = r.pod<int64_t>();
     for (int i = 0; i < FB_MAX_RANK; ++i) t.strides[i] = r.pod<int64_t>();
     t.scalar = r.pod<double>();
+    t.dynamic_mask = r.pod<uint32_t>();
     t.ws_offset = r.pod<int64_t>();
     FB_REQUIRE(r.ok && t.rank >= 1 && t.rank <= FB_MAX_RANK, FB_RUNTIME_FAILURE,
                "artifact payload is malformed");

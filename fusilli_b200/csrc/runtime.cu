@@ -1,6 +1,9 @@
 // Device, buffer and plan entry points of the C ABI (host side).
 #include <cstring>
+#include <map>
+#include <memory>
 #include <mutex>
+#include <vector>
 
 #include "common.h"
 
@@ -71,6 +74,11 @@ using namespace fb;
 struct fb_plan {
   Plan plan;
   int ordinal = 0;
+  // Plans lowered again for concrete extents of the dynamic dims, keyed by the extents of all
+  // arguments. Bounded: shapes past the limit replace the whole set.
+  std::mutex mu;
+  std::map<std::vector<int64_t>, std::unique_ptr<Plan>> shaped;
+  static constexpr size_t kMaxShaped = 64;
 };
 
 FB_EXPORT int32_t fb_abi_version(void) { return FB_ABI_VERSION; }
@@ -296,6 +304,13 @@ static fb_status plan_from_desc(const fb_graph_desc *g, Plan &p) {
       FB_REQUIRE(d.dims[k] >= 1 && d.strides[k] >= 0, FB_INVALID_ARGUMENT,
                  "fb_plan_build: tensor '" + t.name + "' has a non-positive dim or negative stride");
     }
+    t.dynamic_mask = d.dynamic_mask;
+    FB_REQUIRE(d.rank >= 32 || (d.dynamic_mask >> d.rank) == 0, FB_INVALID_ARGUMENT,
+               "fb_plan_build: tensor '" + t.name + "' marks a dim past its rank as dynamic");
+    for (int k = 0; k < d.rank; ++k)
+      FB_REQUIRE(!(d.dynamic_mask >> k & 1) || (d.strides[k] != 0 && d.role != FB_TENSOR_SCALAR),
+                 FB_INVALID_ARGUMENT,
+                 "fb_plan_build: tensor '" + t.name + "' has a dynamic dim with a broadcast stride");
     bool bound = d.role == FB_TENSOR_INPUT || d.role == FB_TENSOR_OUTPUT;
     FB_REQUIRE(bound == (d.arg_index >= 0), FB_INVALID_ARGUMENT,
                "fb_plan_build: tensor '" + t.name + "' role and arg_index disagree");
@@ -351,6 +366,32 @@ FB_EXPORT fb_status fb_plan_build(const fb_graph_desc *graph, uint8_t **bytes, s
 }
 
 FB_EXPORT void fb_bytes_free(uint8_t *bytes) { free(bytes); }
+
+FB_EXPORT fb_status fb_plan_specialize(const uint8_t *bytes, size_t num_bytes, const int64_t *arg_dims,
+                                       int32_t num_args, uint8_t **out_bytes, size_t *out_num_bytes) {
+  clear_error();
+  FB_REQUIRE(out_bytes && out_num_bytes, FB_INVALID_ARGUMENT, "fb_plan_specialize: NULL output argument");
+  *out_bytes = nullptr;
+  *out_num_bytes = 0;
+  FB_REQUIRE(bytes != nullptr && num_bytes > 0, FB_RUNTIME_FAILURE, "fb_plan_specialize: empty artifact");
+  Plan base, shaped;
+  fb_status st = deserialize(bytes, num_bytes, base);
+  if (st != FB_OK) return st;
+  FB_REQUIRE(num_args == base.num_args, FB_VARIANT_PACK_ERROR,
+             "fb_plan_specialize: expected dims of " + std::to_string(base.num_args) + " buffers, got " +
+                 std::to_string(num_args));
+  st = specialize(base, arg_dims, shaped);
+  if (st != FB_OK) return st;
+  std::vector<uint8_t> blob;
+  st = serialize(shaped, blob);
+  if (st != FB_OK) return st;
+  uint8_t *out = static_cast<uint8_t *>(malloc(blob.size()));
+  FB_REQUIRE(out != nullptr, FB_INTERNAL_ERROR, "fb_plan_specialize: out of host memory");
+  memcpy(out, blob.data(), blob.size());
+  *out_bytes = out;
+  *out_num_bytes = blob.size();
+  return FB_OK;
+}
 
 FB_EXPORT fb_status fb_plan_load(fb_device *dev, const uint8_t *bytes, size_t num_bytes,
                                  fb_plan **out) {
@@ -415,12 +456,9 @@ FB_EXPORT fb_status fb_plan_stats_json(fb_plan *plan, char *buf, size_t cap, siz
   return FB_OK;
 }
 
-FB_EXPORT fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *args,
-                                    const size_t *arg_bytes, int32_t num_args, void *workspace,
-                                    size_t workspace_bytes) {
-  clear_error();
-  FB_REQUIRE(plan && dev, FB_INVALID_ARGUMENT, "fb_plan_execute: NULL plan or device");
-  const Plan &p = plan->plan;
+static fb_status execute_plan(const fb_plan *plan, const Plan &p, fb_device *dev, void *const *args,
+                              const size_t *arg_bytes, int32_t num_args, void *workspace,
+                              size_t workspace_bytes) {
   FB_REQUIRE(dev->ordinal == plan->ordinal, FB_INVALID_ARGUMENT,
              "fb_plan_execute: plan was loaded for device " + std::to_string(plan->ordinal) +
                  " but executed on device " + std::to_string(dev->ordinal));
@@ -475,5 +513,68 @@ FB_EXPORT fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *
       return fail(FB_RUNTIME_FAILURE, std::string("kernel launch failed (") +
                                           step_kernel_name(p, s) + "): " + cudaGetErrorString(le));
   }
+  return FB_OK;
+}
+
+FB_EXPORT fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *args,
+                                    const size_t *arg_bytes, int32_t num_args, void *workspace,
+                                    size_t workspace_bytes) {
+  clear_error();
+  FB_REQUIRE(plan && dev, FB_INVALID_ARGUMENT, "fb_plan_execute: NULL plan or device");
+  return execute_plan(plan, plan->plan, dev, args, arg_bytes, num_args, workspace, workspace_bytes);
+}
+
+// The plan for these extents: the loaded one when they are its own, else a specialisation (kept).
+static fb_status shaped_plan(fb_plan *plan, const int64_t *arg_dims, int32_t num_args, const Plan **out) {
+  const Plan &base = plan->plan;
+  FB_REQUIRE(num_args == base.num_args, FB_VARIANT_PACK_ERROR,
+             "expected " + std::to_string(base.num_args) + " buffers, got " + std::to_string(num_args));
+  FB_REQUIRE(arg_dims != nullptr || num_args == 0, FB_INVALID_ARGUMENT, "arg_dims is NULL");
+  bool same = true;
+  std::vector<int64_t> key;
+  for (int a = 0; a < num_args; ++a) {
+    const TensorInfo &t = base.tensors[base.arg_tensor[a]];
+    for (int k = 0; k < t.rank; ++k) {
+      const int64_t v = arg_dims[(size_t)a * FB_MAX_RANK + k];
+      key.push_back(v);
+      same = same && v == t.dims[k];
+    }
+  }
+  if (same) {
+    *out = &base;
+    return FB_OK;
+  }
+  std::lock_guard<std::mutex> lock(plan->mu);
+  auto it = plan->shaped.find(key);
+  if (it == plan->shaped.end()) {
+    auto sp = std::make_unique<Plan>();
+    fb_status st = specialize(base, arg_dims, *sp);
+    if (st != FB_OK) return st;
+    if (plan->shaped.size() >= fb_plan::kMaxShaped) plan->shaped.clear();
+    it = plan->shaped.emplace(std::move(key), std::move(sp)).first;
+  }
+  *out = it->second.get();
+  return FB_OK;
+}
+
+FB_EXPORT fb_status fb_plan_execute_shaped(fb_plan *plan, fb_device *dev, void *const *args,
+                                           const size_t *arg_bytes, const int64_t *arg_dims,
+                                           int32_t num_args, void *workspace, size_t workspace_bytes) {
+  clear_error();
+  FB_REQUIRE(plan && dev, FB_INVALID_ARGUMENT, "fb_plan_execute_shaped: NULL plan or device");
+  const Plan *p = nullptr;
+  fb_status st = shaped_plan(plan, arg_dims, num_args, &p);
+  if (st != FB_OK) return st;
+  return execute_plan(plan, *p, dev, args, arg_bytes, num_args, workspace, workspace_bytes);
+}
+
+FB_EXPORT fb_status fb_plan_workspace_size_shaped(fb_plan *plan, const int64_t *arg_dims, int32_t num_args,
+                                                  size_t *bytes) {
+  clear_error();
+  FB_REQUIRE(plan && bytes, FB_INVALID_ARGUMENT, "fb_plan_workspace_size_shaped: NULL argument");
+  const Plan *p = nullptr;
+  fb_status st = shaped_plan(plan, arg_dims, num_args, &p);
+  if (st != FB_OK) return st;
+  *bytes = p->workspace_bytes;
   return FB_OK;
 }

@@ -188,6 +188,7 @@ class TensorAttr:
         self._virtual = False
         self._scalar = False
         self.scalarValue = None
+        self._dynamic: List[int] = []  # sorted, unique logical dim indices (tensor_attributes.h:512-570)
         if scalar is not None:
             self._scalar = True
             self.scalarValue = scalar
@@ -205,6 +206,9 @@ class TensorAttr:
     def setIsVirtual(self, v): self._virtual = bool(v); return self
     def setOutput(self, v): return self.setIsVirtual(not v)
     def setIsScalar(self, v): self._scalar = bool(v); return self
+    def setDynamicDim(self, index): return self.setDynamicDims(self._dynamic + [int(index)])
+    def setDynamicDims(self, indices): self._dynamic = sorted({int(i) for i in indices}); return self
+    def clearDynamicDims(self): self._dynamic = []; return self
 
     # getters -----------------------------------------------------------------
     def getName(self): return self.name
@@ -214,6 +218,9 @@ class TensorAttr:
     def isVirtual(self): return self._virtual
     def isScalar(self): return self._scalar
     def getScalarValue(self): return self.scalarValue
+    def getDynamicDims(self): return self._dynamic
+    def hasDynamicDims(self): return bool(self._dynamic)
+    def isDynamicDim(self, index): return int(index) in self._dynamic
 
     def getVolume(self) -> int:
         return math.prod(self.dim)
@@ -268,6 +275,17 @@ class TensorAttr:
         _require(bool(self.stride), ErrorCode.AttributeNotSet, n + " strides not set")
         _require(len(self.dim) == len(self.stride), ErrorCode.InvalidAttribute,
                  n + " uses dim and stride of different dimensionality")
+        for d in self._dynamic:
+            _require(d < len(self.dim), ErrorCode.InvalidAttribute,
+                     n + f" has dynamic dim index {d} out of range for rank {len(self.dim)}")
+            _require(self.stride[d] != 0, ErrorCode.InvalidAttribute,
+                     n + f" has dynamic dim at index {d} with stride 0 (broadcast stride), which "
+                         "is not supported")
+            _require(self.dim[d] != 1, ErrorCode.InvalidAttribute,
+                     n + f" has dynamic dim at index {d} with representative size 1, which is "
+                         "not supported")
+        _require(not (self.hasBroadcastDims() and self.hasDynamicDims()), ErrorCode.InvalidAttribute,
+                 n + " has dynamic dimensions on a tensor with broadcast strides, which is not supported")
         _require(self.hasValidPhysicalRepresentation(), ErrorCode.InvalidAttribute,
                  n + " has invalid physical representation. It must be a valid "
                      "permutation of the logical dimensions")

@@ -28,7 +28,8 @@ class fb_tensor_desc(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("dtype", ctypes.c_int32), ("role", ctypes.c_int32),
                 ("rank", ctypes.c_int32), ("arg_index", ctypes.c_int32),
                 ("dims", ctypes.c_int64 * FB_MAX_RANK), ("strides", ctypes.c_int64 * FB_MAX_RANK),
-                ("scalar_value", ctypes.c_double)]
+                ("scalar_value", ctypes.c_double), ("dynamic_mask", ctypes.c_uint32),
+                ("reserved", ctypes.c_int32)]
 
 
 class fb_node_desc(ctypes.Structure):
@@ -77,6 +78,11 @@ ABI_SYMBOLS = [
     ("fb_plan_num_launches", _I32, [_VP, ctypes.POINTER(_I32)]),
     ("fb_plan_stats_json", _I32, [_VP, ctypes.c_char_p, _SZ, ctypes.POINTER(_SZ)]),
     ("fb_plan_execute", _I32, [_VP, _VP, ctypes.POINTER(_VP), ctypes.POINTER(_SZ), _I32, _VP, _SZ]),
+    ("fb_plan_execute_shaped", _I32, [_VP, _VP, ctypes.POINTER(_VP), ctypes.POINTER(_SZ),
+                                      ctypes.POINTER(ctypes.c_int64), _I32, _VP, _SZ]),
+    ("fb_plan_specialize", _I32, [ctypes.c_char_p, _SZ, ctypes.POINTER(ctypes.c_int64), _I32,
+                                  ctypes.POINTER(ctypes.POINTER(ctypes.c_uint8)), ctypes.POINTER(_SZ)]),
+    ("fb_plan_workspace_size_shaped", _I32, [_VP, ctypes.POINTER(ctypes.c_int64), _I32, ctypes.POINTER(_SZ)]),
     ("fb_conv_wgrad_static_scratch_bytes", _SZ, []),
     ("fb_conv_wgrad_static", _I32, [_VP, _VP, _VP, _VP] + [_I32] * 15),
 ]
@@ -159,9 +165,11 @@ class Handle:
 class Buffer:
     """fusilli::Buffer (buffer.h:31-81)."""
 
-    def __init__(self, ptr, handle=None):
+    def __init__(self, ptr, handle=None, shape=None):
         self._ptr = ptr
         self._handle = handle  # keeps the device alive as long as the buffer
+        # dims of the dense (physical order) array; graphs with dynamic dims read them at execute
+        self.shape: Optional[List[int]] = [int(v) for v in shape] if shape is not None else None
 
     @staticmethod
     def allocate(handle: Handle, shape: Sequence[int], data: np.ndarray) -> "Buffer":
@@ -175,6 +183,7 @@ class Buffer:
                                f"Buffer::allocate failed: bufferData size ({data.size}) does not match "
                                f"product of bufferShape dimensions ({expected})")
         buf = Buffer.allocateRaw(handle, data.nbytes)
+        buf.shape = [int(v) for v in shape]
         _check(lib().fb_buffer_h2d(handle._ptr, buf._ptr, data.ctypes.data_as(_VP), data.nbytes))
         return buf
 
@@ -188,14 +197,14 @@ class Buffer:
         return Buffer(out, handle)
 
     @staticmethod
-    def importPointer(handle: Handle, devicePtr: int, sizeInBytes: int) -> "Buffer":
+    def importPointer(handle: Handle, devicePtr: int, sizeInBytes: int, shape=None) -> "Buffer":
         """Buffer::import of caller-owned device memory (e.g. a torch tensor)."""
         if not devicePtr:
             raise FusilliError(ErrorCode.RuntimeFailure,
                                "Buffer::import failed as externalBufferView* is NULL")
         out = _VP()
         _check(lib().fb_buffer_wrap(handle._ptr, _VP(devicePtr), sizeInBytes, ctypes.byref(out)))
-        return Buffer(out, handle)
+        return Buffer(out, handle, shape)
 
     def write(self, handle: Handle, data: np.ndarray) -> None:
         data = np.ascontiguousarray(data)
@@ -305,6 +314,8 @@ class Graph(GraphBase):
             for k in range(len(t.dim)):
                 d.dims[k] = t.dim[k]
                 d.strides[k] = t.stride[k]
+            for k in t.getDynamicDims():
+                d.dynamic_mask |= 1 << k
             if t.isScalar():
                 d.role = 3
                 d.scalar_value = float(t.getScalarValue())
@@ -411,7 +422,38 @@ class Graph(GraphBase):
             ptrs[i] = b.ptr()
             sizes[i] = b.size()
         ws_ptr, ws_size = (workspace.ptr(), workspace.size()) if workspace is not None else (None, 0)
+        if any(t.hasDynamicDims() for t in self._arg_tensors):
+            dims = self._runtime_dims(variantPack)
+            _check(lib().fb_plan_execute_shaped(self._plan, handle._ptr, ptrs, sizes, dims, n, ws_ptr, ws_size))
+            return
         _check(lib().fb_plan_execute(self._plan, handle._ptr, ptrs, sizes, n, ws_ptr, ws_size))
+
+    def _runtime_dims(self, variantPack):
+        """FB_MAX_RANK logical extents per argument: a tensor's own dims, or for one with dynamic
+        dims the shape of this call's buffer (physical order, as the reference's buffer views)."""
+        n = len(self._arg_tensors)
+        dims = (ctypes.c_int64 * (n * FB_MAX_RANK))(*([1] * (n * FB_MAX_RANK)))
+        for i, t in enumerate(self._arg_tensors):
+            logical = list(t.dim)
+            if t.hasDynamicDims():
+                shape = variantPack[t].shape
+                if shape is None or len(shape) != len(logical):
+                    raise FusilliError(ErrorCode.InvalidArgument,
+                                       f"Buffer for tensor '{t.name}' carries no shape of rank {len(logical)}")
+                for pos, src in enumerate(t.getLogicalToPhysicalPermuteOrder()):
+                    logical[src] = int(shape[pos])
+            for k, v in enumerate(logical):
+                dims[i * FB_MAX_RANK + k] = v
+        return dims
+
+    def getWorkspaceSizeFor(self, variantPack) -> int:
+        """Workspace bytes for the shapes of `variantPack`'s buffers (dynamic graphs)."""
+        if not self._plan:
+            raise FusilliError(ErrorCode.NotCompiled, "Graph must be compiled before being executed")
+        out = _SZ()
+        _check(lib().fb_plan_workspace_size_shaped(self._plan, self._runtime_dims(variantPack),
+                                                   len(self._arg_tensors), ctypes.byref(out)))
+        return out.value
 
     def __del__(self):
         try:

@@ -98,6 +98,7 @@ public:
     fb_buffer *b = nullptr;
     FUSILLI_FB_CALL(fb_buffer_alloc(handle.device(), expected * sizeof(T), &b));
     Buffer out(b);
+    out.shape_ = bufferShape;
     FUSILLI_FB_CALL(fb_buffer_h2d(handle.device(), b, bufferData.data(), expected * sizeof(T)));
     return ok(std::move(out));
   }
@@ -125,6 +126,14 @@ public:
     FUSILLI_FB_CALL(fb_buffer_wrap(handle.device(), devicePtr, sizeInBytes, &b));
     return ok(Buffer(b));
   }
+  // The same with the dims of the dense array behind the pointer, which a graph with dynamic dims
+  // reads at execute (the reference's imported buffer views carry their shape, runtime.h:596-611).
+  static ErrorOr<Buffer> import(const Handle &handle, void *devicePtr, size_t sizeInBytes,
+                                const std::vector<size_t> &bufferShape) {
+    FUSILLI_ASSIGN_OR_RETURN(Buffer out, import(handle, devicePtr, sizeInBytes));
+    out.shape_ = bufferShape;
+    return ok(std::move(out));
+  }
 
   // Device -> host copy of the whole buffer; synchronises the handle's stream.
   template <typename T> ErrorObject read(const Handle &handle, std::vector<T> &outData) {
@@ -139,14 +148,21 @@ public:
   operator fb_buffer *() const { return buf_; }
   void *devicePointer() const { return fb_buffer_ptr(buf_); }
   size_t sizeInBytes() const { return fb_buffer_size(buf_); }
+  // Dims of the dense (physical order) array the buffer was allocated for; empty when unknown.
+  const std::vector<size_t> &getShape() const { return shape_; }
+  Buffer &setShape(const std::vector<size_t> &shape) {
+    shape_ = shape;
+    return *this;
+  }
 
   Buffer(const Buffer &) = delete;
   Buffer &operator=(const Buffer &) = delete;
-  Buffer(Buffer &&o) noexcept : buf_(std::exchange(o.buf_, nullptr)) {}
+  Buffer(Buffer &&o) noexcept : buf_(std::exchange(o.buf_, nullptr)), shape_(std::move(o.shape_)) {}
   Buffer &operator=(Buffer &&o) noexcept {
     if (this != &o) {
       if (buf_) fb_buffer_release(buf_);
       buf_ = std::exchange(o.buf_, nullptr);
+      shape_ = std::move(o.shape_);
     }
     return *this;
   }
@@ -157,6 +173,7 @@ public:
 private:
   explicit Buffer(fb_buffer *b) : buf_(b) {}
   fb_buffer *buf_ = nullptr;
+  std::vector<size_t> shape_;
 };
 
 } // namespace fusilli

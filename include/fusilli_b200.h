@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define FB_ABI_VERSION 1
+#define FB_ABI_VERSION 2
 #define FB_MAX_RANK 8
 #define FB_MAX_NODE_INPUTS 4
 #define FB_MAX_NODE_OUTPUTS 3
@@ -175,7 +175,11 @@ enum {
  * position of the tensor's buffer in fb_plan_execute's pointer list (non-virtual
  * outputs sorted by name first, then non-scalar inputs sorted by name -- the
  * argument order of the reference's generated function,
- * include/fusilli/backend/runtime.h:426-457); -1 for virtual and scalar. */
+ * include/fusilli/backend/runtime.h:426-457); -1 for virtual and scalar.
+ * Bit k of `dynamic_mask` marks logical dim k as dynamic
+ * (TensorAttr::setDynamicDims, tensor_attributes.h:512-570): `dims` and
+ * `strides` then hold the representative extent and the dense layout pattern,
+ * and fb_plan_execute_shaped takes the extent of each call. */
 typedef struct fb_tensor_desc {
   const char *name;
   int32_t dtype;
@@ -185,6 +189,8 @@ typedef struct fb_tensor_desc {
   int64_t dims[FB_MAX_RANK];
   int64_t strides[FB_MAX_RANK];
   double scalar_value; /* role == FB_TENSOR_SCALAR only */
+  uint32_t dynamic_mask;
+  int32_t reserved;
 } fb_tensor_desc;
 
 /* One node. Tensor slots by op (index into fb_graph_desc.tensors, -1 = absent):
@@ -312,6 +318,33 @@ fb_status fb_plan_stats_json(fb_plan *plan, char *buf, size_t cap,
 fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *args,
                           const size_t *arg_bytes, int32_t num_args,
                           void *workspace, size_t workspace_bytes);
+/* fb_plan_execute for a plan whose graph has dynamic dims. `arg_dims` holds
+ * FB_MAX_RANK logical extents per buffer (row i = the tensor whose arg_index
+ * is i; entries past the tensor's rank are ignored): static dims must equal
+ * the plan's, dynamic ones give this call's extent. The extents of virtual
+ * tensors follow from the nodes' shape rules, strides are regenerated as the
+ * dense layout the representative strides describe, and the kernels are chosen
+ * again for the concrete shape; the result is kept in the plan, keyed by the
+ * extents, so a repeated shape costs a lookup. Extents that the inputs do not
+ * imply (an output buffer of the wrong shape) are FB_INVALID_ARGUMENT. The
+ * workspace must cover the concrete shape; fb_plan_workspace_size reports the
+ * size for the representative extents (the reference likewise has no
+ * runtime-sized workspace query, runtime.h:361-369). A plan without dynamic
+ * dims accepts only its own dims. */
+fb_status fb_plan_execute_shaped(fb_plan *plan, fb_device *dev,
+                                 void *const *args, const size_t *arg_bytes,
+                                 const int64_t *arg_dims, int32_t num_args,
+                                 void *workspace, size_t workspace_bytes);
+/* The same specialisation without a device: artifact bytes in, artifact bytes
+ * for the given extents out (free with fb_bytes_free). The result equals what
+ * fb_plan_build gives for a graph declared with those extents as its
+ * representative dims. */
+fb_status fb_plan_specialize(const uint8_t *bytes, size_t num_bytes,
+                             const int64_t *arg_dims, int32_t num_args,
+                             uint8_t **out_bytes, size_t *out_num_bytes);
+/* Scratch bytes fb_plan_execute_shaped needs for the given extents. */
+fb_status fb_plan_workspace_size_shaped(fb_plan *plan, const int64_t *arg_dims,
+                                        int32_t num_args, size_t *bytes);
 /* Error word written by kernels whose bounded waits ran out (0 = none). Reads
  * it with a stream synchronise. */
 fb_status fb_device_kernel_error(fb_device *dev, uint32_t *error_word);

@@ -216,3 +216,67 @@ TEST_CASE("conv wgrad plan asks for a workspace and refuses to run without it", 
   REQUIRE(at(63, 63, 0, 0) == float(n * (hw - 1) * (hw - 1)));
   REQUIRE(at(5, 9, 1, 0) == float(n * hw * (hw - 1)));
 }
+
+TEST_CASE("one plan with a dynamic batch serves channels-last buffers of several batch sizes", "[dynamic]") {
+  const int64_t n = 8, c = 64, hw = 16, kk = 64;
+  FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));
+  Graph g;
+  g.setName("cpp_dynamic_conv").setIODataType(DataType::BFloat16).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto xT = g.tensor(TensorAttr().setName("x").setDim({n, c, hw, hw}).setStride({c * hw * hw, 1, c * hw, c}).setDynamicDims({0}));
+  auto wT = g.tensor(TensorAttr().setName("w").setDim({kk, c, 3, 3}).setStride({c * 9, 1, c * 3, c}));
+  ConvFPropAttr conv;
+  conv.setName("conv").setPadding({1, 1}).setStride({1, 1}).setDilation({1, 1});
+  auto yT = g.convFProp(xT, wT, conv);
+  yT->setDynamicDims({0});
+  PointwiseAttr relu;
+  relu.setName("relu").setMode(PointwiseAttr::Mode::RELU_FWD);
+  auto zT = g.pointwise(yT, relu);
+  zT->setDynamicDims({0}).setOutput(true);
+  FUSILLI_REQUIRE_OK(g.validate());
+  FUSILLI_REQUIRE_OK(g.compile(handle, /*remove=*/true));
+  FUSILLI_REQUIRE_ASSIGN(auto text, g.readCompilationCacheFile(CachedAssetsType::Input));
+  REQUIRE(text.find("dynamic=1") != std::string::npos);
+  FUSILLI_REQUIRE_ASSIGN(auto ws, g.getWorkspaceSize());
+  FUSILLI_REQUIRE_ASSIGN(auto wsBuf, allocateWorkspace(handle, ws));
+  FUSILLI_REQUIRE_ASSIGN(auto wBuf, allocateBufferOfType(handle, wT, DataType::BFloat16, 1.0));
+
+  for (int64_t rn : {int64_t(1), int64_t(3), n, int64_t(3)}) {
+    // buffer shapes are in physical (NHWC) order, as the reference's helpers allocate them
+    const std::vector<size_t> xShape = {size_t(rn), size_t(hw), size_t(hw), size_t(c)};
+    const std::vector<size_t> zShape = {size_t(rn), size_t(hw), size_t(hw), size_t(kk)};
+    FUSILLI_REQUIRE_ASSIGN(auto xRaw, Buffer::allocate(handle, xShape, std::vector<bf16>(rn * c * hw * hw, bf16(1.0f))));
+    FUSILLI_REQUIRE_ASSIGN(auto zRaw, Buffer::allocate(handle, zShape, std::vector<bf16>(rn * kk * hw * hw, bf16(-1.0f))));
+    auto xBuf = share(std::move(xRaw)), zBuf = share(std::move(zRaw));
+    Graph::VariantPack pack = {{xT, xBuf}, {wT, wBuf}, {zT, zBuf}};
+    FUSILLI_REQUIRE_OK(g.execute(handle, pack, wsBuf));
+    std::vector<bf16> z;
+    FUSILLI_REQUIRE_OK(zBuf->read(handle, z));
+    REQUIRE(z.size() == size_t(rn * kk * hw * hw));
+    auto at = [&](int64_t ni, int64_t ki, int64_t y, int64_t x) { return float(z[((ni * hw + y) * hw + x) * kk + ki]); };
+    REQUIRE(at(0, 0, 0, 0) == 4.f * c);
+    REQUIRE(at(rn - 1, 63, 8, 8) == 9.f * c);
+    REQUIRE(at(rn - 1, 17, 15, 15) == 4.f * c);
+    REQUIRE(at(rn / 2, 5, 0, 7) == 6.f * c);
+  }
+
+  // an imported pointer with its shape works; without a shape a single dynamic dim follows from the size
+  const int64_t rn = 2;
+  FUSILLI_REQUIRE_ASSIGN(auto xOwned, Buffer::allocate(handle, {size_t(rn * c * hw * hw)}, std::vector<bf16>(rn * c * hw * hw, bf16(1.0f))));
+  FUSILLI_REQUIRE_ASSIGN(auto zOwned, Buffer::allocateRaw(handle, size_t(rn * kk * hw * hw) * sizeof(bf16)));
+  FUSILLI_REQUIRE_ASSIGN(auto xImp, Buffer::import(handle, xOwned.devicePointer(), xOwned.sizeInBytes(),
+                                                   {size_t(rn), size_t(hw), size_t(hw), size_t(c)}));
+  FUSILLI_REQUIRE_ASSIGN(auto zImp, Buffer::import(handle, zOwned.devicePointer(), zOwned.sizeInBytes()));
+  Graph::VariantPack pack = {{xT, share(std::move(xImp))}, {wT, wBuf}, {zT, share(std::move(zImp))}};
+  FUSILLI_REQUIRE_OK(g.execute(handle, pack, wsBuf));
+  std::vector<bf16> z;
+  FUSILLI_REQUIRE_OK(zOwned.read(handle, z));
+  REQUIRE(float(z[((1 * hw + 8) * hw + 8) * kk + 9]) == 9.f * c);
+
+  // an output buffer whose batch is not the input's is refused before anything is launched
+  FUSILLI_REQUIRE_ASSIGN(auto wrong, Buffer::allocate(handle, {size_t(3), size_t(hw), size_t(hw), size_t(kk)},
+                                                      std::vector<bf16>(3 * kk * hw * hw, bf16(0.0f))));
+  pack[zT] = share(std::move(wrong));
+  auto st = g.execute(handle, pack, wsBuf);
+  REQUIRE(st.getCode() == ErrorCode::InvalidArgument);
+  REQUIRE(st.getMessage().find("imply") != std::string::npos);
+}

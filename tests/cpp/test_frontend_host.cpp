@@ -178,3 +178,43 @@ TEST_CASE("unsupported node kinds fail loudly at plan build, never fall back", "
   auto r = g.compileToArtifact(Backend::CUDA, /*remove=*/true);
   REQUIRE(isError(r));
 }
+
+TEST_CASE("graphs with dynamic dims build plans without a device", "[graph][dynamic]") {
+  Graph g;
+  g.setName("dynamic_rows").setIODataType(DataType::Float).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto a = g.tensor(TensorAttr().setName("a").setDim({64, 32}).setStride({32, 1}).setDynamicDims({0}));
+  auto b = g.tensor(TensorAttr().setName("b").setDim({32, 16}).setStride({16, 1}));
+  MatmulAttr mm;
+  mm.setName("mm");
+  auto c = g.matmul(a, b, mm);
+  c->setDynamicDims({0}).setOutput(true);
+  FUSILLI_REQUIRE_OK(g.validate());
+  FUSILLI_REQUIRE_ASSIGN(auto bytes, g.compileToArtifact(Backend::CUDA, /*remove=*/true));
+  FUSILLI_REQUIRE_OK(fromStatus(fb_plan_check(bytes.data(), bytes.size())));
+  // specialising for 5 rows gives the plan of the graph declared with 5 rows
+  // argument order: outputs by name, then inputs by name -> mm_C, a, b
+  int64_t dims[3 * FB_MAX_RANK] = {};
+  for (auto &d : dims) d = 1;
+  dims[0] = 5, dims[1] = 16;
+  dims[FB_MAX_RANK] = 5, dims[FB_MAX_RANK + 1] = 32;
+  dims[2 * FB_MAX_RANK] = 32, dims[2 * FB_MAX_RANK + 1] = 16;
+  uint8_t *out = nullptr;
+  size_t n = 0;
+  FUSILLI_REQUIRE_OK(fromStatus(fb_plan_specialize(bytes.data(), bytes.size(), dims, 3, &out, &n)));
+  std::vector<uint8_t> shaped(out, out + n);
+  fb_bytes_free(out);
+  Graph five;
+  five.setName("dynamic_rows").setIODataType(DataType::Float).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto a5 = five.tensor(TensorAttr().setName("a").setDim({5, 32}).setStride({32, 1}).setDynamicDims({0}));
+  auto b5 = five.tensor(TensorAttr().setName("b").setDim({32, 16}).setStride({16, 1}));
+  MatmulAttr mm5;
+  mm5.setName("mm");
+  auto c5 = five.matmul(a5, b5, mm5);
+  c5->setDynamicDims({0}).setOutput(true);
+  FUSILLI_REQUIRE_OK(five.validate());
+  FUSILLI_REQUIRE_ASSIGN(auto direct, five.compileToArtifact(Backend::CUDA, /*remove=*/true));
+  REQUIRE(shaped == direct);
+  // a static dim that differs is refused
+  dims[FB_MAX_RANK + 1] = 40;
+  REQUIRE(fb_plan_specialize(bytes.data(), bytes.size(), dims, 3, &out, &n) == FB_INVALID_ARGUMENT);
+}

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} declared in fusilli_b200.h but not exported"
     bound = {n for n, _, _ in runtime.ABI_SYMBOLS}
     assert declared == bound, (declared - bound, bound - declared)
-    assert runtime.lib().fb_abi_version() == 1
+    assert runtime.lib().fb_abi_version() == 2
 
 
 def test_status_codes_match_error_codes():

@@ -234,6 +234,19 @@ public:
     nodes_.push_back(std::make_unique<ReductionNode>(std::move(a), context));
     return y;
   }
+  // Accepted as in the reference (graph.h:1195-1227); compileToArtifact refuses graphs that hold one.
+  std::vector<TensorPtr> customOp(std::vector<TensorPtr> ins, CustomOpAttr &a) {
+    if (a.getName().empty()) a.setName("custom_op_" + std::to_string(nodes_.size()));
+    for (size_t i = 0; i < ins.size(); ++i)
+      if (ins[i] && ins[i]->getName().empty()) ins[i]->setName(a.getName() + "_IN_" + std::to_string(i));
+    std::vector<TensorPtr> outs;
+    for (size_t i = 0; i < a.getNumOutputs(); ++i) outs.push_back(outputTensor(a.getName() + "_OUT_" + std::to_string(i)));
+    auto node = std::make_unique<CustomOpNode>(std::move(a), context);
+    node->inputs = std::move(ins);
+    node->outputs = outs;
+    nodes_.push_back(std::move(node));
+    return outs;
+  }
   TensorPtr pointwise(const TensorPtr &in0, PointwiseAttr &a) { return addPointwise({in0, nullptr, nullptr}, 1, a); }
   TensorPtr pointwise(const TensorPtr &in0, const TensorPtr &in1, PointwiseAttr &a) {
     return addPointwise({in0, in1, nullptr}, 2, a);

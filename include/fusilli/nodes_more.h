@@ -516,6 +516,51 @@ public:
   }
 };
 
+// ---- custom op (reference attributes/custom_op_attributes.h:23-110, node/custom_op_node.h) ------
+// A node whose body is a piece of torch-dialect MLIR supplied by the user. The builders and
+// validate() accept it as the reference does (its checks need no compiler); this backend has no
+// MLIR compiler, so building a plan for a graph that holds one is refused with NotImplemented.
+class CustomOpAttr {
+public:
+  CustomOpAttr &setName(const std::string &name) { name_ = name; return *this; }
+  CustomOpAttr &setMlir(const std::string &mlir) { mlir_ = mlir; return *this; }
+  CustomOpAttr &setNumOutputs(size_t n) { numOutputs_ = n; return *this; }
+  const std::string &getName() const { return name_; }
+  const std::string &getMlir() const { return mlir_; }
+  size_t getNumOutputs() const { return numOutputs_; }
+
+private:
+  std::string name_, mlir_;
+  size_t numOutputs_ = 0;
+};
+
+class CustomOpNode : public INode {
+public:
+  CustomOpAttr customOpAttr;
+  std::vector<TensorPtr> inputs, outputs;
+  CustomOpNode(CustomOpAttr &&a, const Context &ctx) : INode(ctx), customOpAttr(std::move(a)) {}
+  const std::string &getName() const override { return customOpAttr.getName(); }
+  Type getType() const override { return Type::Custom; }
+  ErrorObject preValidateNode() const override {
+    FUSILLI_RETURN_ERROR_IF(customOpAttr.getMlir().empty(), ErrorCode::AttributeNotSet, "CustomOp MLIR not set");
+    FUSILLI_RETURN_ERROR_IF(inputs.empty(), ErrorCode::AttributeNotSet, "CustomOp inputs not set");
+    FUSILLI_RETURN_ERROR_IF(outputs.empty(), ErrorCode::AttributeNotSet, "CustomOp outputs not set");
+    for (size_t i = 0; i < inputs.size(); ++i) {
+      FUSILLI_RETURN_ERROR_IF(!inputs[i], ErrorCode::AttributeNotSet, "CustomOp input " + std::to_string(i) + " is null");
+      FUSILLI_RETURN_ERROR_IF(inputs[i]->isScalar(), ErrorCode::InvalidAttribute,
+                              "CustomOp input " + std::to_string(i) + " is scalar (not supported)");
+    }
+    for (size_t i = 0; i < outputs.size(); ++i)
+      FUSILLI_RETURN_ERROR_IF(outputs[i]->isScalar(), ErrorCode::InvalidAttribute,
+                              "CustomOp output " + std::to_string(i) + " is scalar (not supported)");
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    for (auto &t : inputs) t->fillFromContext(context);
+    return ok();
+  }
+};
+
 } // namespace fusilli
 
 #endif // FUSILLI_NODES_MORE_H

@@ -73,6 +73,21 @@ REFERENCE_SAMPLES = [
     "samples/dynamic_shapes/sdpa_basic_dynamic_sequence.cpp",
 ]
 
+# The SDPA samples share one helper translation unit (samples/sdpa_utils.cpp: graph set-up, a scalar
+# reference, and a custom-op variant that this backend accepts at build time and refuses at
+# compile); it is compiled once and linked into each of them. The dropout sample is disabled in
+# the reference's own build.
+REFERENCE_SDPA_UTILS = "samples/sdpa_utils.cpp"
+REFERENCE_SDPA_SAMPLES = [
+    "samples/sdpa/sdpa_fprop_basic_mha.cpp",
+    "samples/sdpa/sdpa_fprop_causal.cpp",
+    "samples/sdpa/sdpa_fprop_cross_attn.cpp",
+    "samples/sdpa/sdpa_fprop_custom_scale.cpp",
+    "samples/sdpa/sdpa_fprop_gqa.cpp",
+    "samples/sdpa/sdpa_fprop_gqa_hk_ne_hv.cpp",
+    "samples/sdpa/sdpa_fprop_with_mask.cpp",
+]
+
 # Reference unit tests that need no device (attribute and node validation, context, tensors).
 REFERENCE_HOST_TESTS = [
     "tests/test_attributes.cpp",
@@ -128,28 +143,52 @@ def _header_deps():
     return deps
 
 
-def _compile(src, exe, extra_includes, hdeps):
-    if _newer(exe, [src] + hdeps):
+def _compile(src, exe, extra_includes, hdeps, objects=()):
+    if _newer(exe, [src] + list(objects) + hdeps):
         return exe, 0, "up to date"
     cflags, ldflags = _flags()
-    cmd = [CXX] + cflags + ["-I" + i for i in extra_includes] + [src, "-o", exe] + ldflags
+    cmd = [CXX] + cflags + ["-I" + i for i in extra_includes] + [src] + list(objects) + ["-o", exe] + ldflags
     p = subprocess.run(cmd, capture_output=True, text=True)
     return exe, p.returncode, p.stderr[-4000:]
 
 
+def _compile_object(src, obj, extra_includes, hdeps):
+    """A helper translation unit without the shim's main()."""
+    if _newer(obj, [src] + hdeps):
+        return obj, 0, "up to date"
+    cflags, _ = _flags()
+    cmd = [CXX] + cflags + ["-DCATCH_SHIM_NO_MAIN", "-c"] + ["-I" + i for i in extra_includes] + [src, "-o", obj]
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    return obj, p.returncode, p.stderr[-4000:]
+
+
+def _sdpa_utils():
+    """(source, object, include dirs) of the SDPA samples' shared helper, or None."""
+    src = os.path.join(REFERENCE, REFERENCE_SDPA_UTILS)
+    if not os.path.exists(src):
+        return None
+    return src, os.path.join(OUT, "ref_sdpa_utils.o"), [os.path.dirname(src)]
+
+
 def jobs():
-    """(source, executable, extra include dirs) for everything that can be built here."""
+    """(source, executable, extra include dirs, extra objects) for everything that can be built here."""
     out = []
     for s in OWN_SOURCES:
         src = os.path.join(HERE, s)
         if os.path.exists(src):
-            out.append((src, os.path.join(OUT, "own_" + os.path.splitext(s)[0]), []))
+            out.append((src, os.path.join(OUT, "own_" + os.path.splitext(s)[0]), [], []))
     if os.path.isdir(REFERENCE):
         for rel in REFERENCE_SAMPLES:
             src = os.path.join(REFERENCE, rel)
             if os.path.exists(src):
                 name = os.path.splitext(os.path.basename(rel))[0]
-                out.append((src, os.path.join(OUT, "ref_" + name), [os.path.dirname(src)]))
+                out.append((src, os.path.join(OUT, "ref_" + name), [os.path.dirname(src)], []))
+        util = _sdpa_utils()
+        for rel in REFERENCE_SDPA_SAMPLES if util else []:
+            src = os.path.join(REFERENCE, rel)
+            if os.path.exists(src):
+                name = os.path.splitext(os.path.basename(rel))[0]
+                out.append((src, os.path.join(OUT, "ref_" + name), [os.path.dirname(src)] + util[2], [util[1]]))
         # The unit tests include "utils.h", which the compiler looks up beside the including file
         # first. They are therefore compiled through a symbolic link in _build/links/, so that the
         # helper header of tests/cpp/shim/ is the one found. The link is not a copy of the source.
@@ -163,14 +202,14 @@ def jobs():
                     os.remove(link)
                 os.symlink(src, link)
                 name = os.path.splitext(os.path.basename(rel))[0]
-                out.append((link, os.path.join(OUT, "ref_" + name), []))
+                out.append((link, os.path.join(OUT, "ref_" + name), [], []))
     return out
 
 
 def expected_programs():
     """Names of every program the lists above describe (built or not)."""
     own = ["own_" + os.path.splitext(s)[0] for s in OWN_SOURCES]
-    ref_dev = ["ref_" + os.path.splitext(os.path.basename(r))[0] for r in REFERENCE_SAMPLES]
+    ref_dev = ["ref_" + os.path.splitext(os.path.basename(r))[0] for r in REFERENCE_SAMPLES + REFERENCE_SDPA_SAMPLES]
     ref_host = ["ref_" + os.path.splitext(os.path.basename(r))[0] for r in REFERENCE_HOST_TESTS]
     return own, ref_dev, ref_host
 
@@ -183,8 +222,13 @@ def build(parallel=None, only=None):
     todo = [j for j in jobs() if only is None or fnmatch.fnmatch(os.path.basename(j[1]), only)]
     hdeps = _header_deps()
     failed = []
+    util = _sdpa_utils()
+    if util and os.path.isdir(REFERENCE) and any(objs for _, _, _, objs in todo):
+        obj, rc, msg = _compile_object(util[0], util[1], util[2], hdeps)
+        if rc != 0:
+            failed.append((obj, msg))
     with cf.ThreadPoolExecutor(max_workers=parallel or os.cpu_count() or 4) as ex:
-        futs = [ex.submit(_compile, s, e, inc, hdeps) for s, e, inc in todo]
+        futs = [ex.submit(_compile, s, e, inc, hdeps, objs) for s, e, inc, objs in todo if not failed]
         for f in cf.as_completed(futs):
             exe, rc, msg = f.result()
             if rc != 0:
@@ -194,7 +238,7 @@ def build(parallel=None, only=None):
         sys.stderr.write("FAILED %s\n%s\n" % (os.path.basename(exe), msg))
     if failed:
         raise RuntimeError("%d C++ test program(s) failed to build" % len(failed))
-    return [e for _, e, _ in todo]
+    return [e for _, e, _, _ in todo]
 
 
 if __name__ in ("__main__", "__graft_build__"):

@@ -210,4 +210,8 @@ template <typename T, typename... R> inline std::vector<std::decay_t<T>> values(
 // Arguments may hold braced lists with commas, so they are only ever passed on whole.
 #define GENERATE(...) catch_shim::generate(__COUNTER__, catch_shim::values(__VA_ARGS__))
 
+// A second translation unit of the same program (a shared helper) is compiled with
+// -DCATCH_SHIM_NO_MAIN; the registry and counters above are inline and therefore shared.
+#ifndef CATCH_SHIM_NO_MAIN
 int main() { return catch_shim::run_all(); }
+#endif

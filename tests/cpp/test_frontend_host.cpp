@@ -218,3 +218,45 @@ TEST_CASE("graphs with dynamic dims build plans without a device", "[graph][dyna
   dims[FB_MAX_RANK + 1] = 40;
   REQUIRE(fb_plan_specialize(bytes.data(), bytes.size(), dims, 3, &out, &n) == FB_INVALID_ARGUMENT);
 }
+
+TEST_CASE("custom ops are accepted by the builders and refused when the plan is built", "[custom_op]") {
+  Graph g;
+  g.setName("custom").setIODataType(DataType::Float).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto a = g.tensor(TensorAttr().setDim({4, 8}).setStride({8, 1}));
+  CustomOpAttr attr;
+  attr.setMlir("func.func private @{FUNC_NAME}() { return }").setNumOutputs(2);
+  auto outs = g.customOp({a}, attr);
+  REQUIRE(outs.size() == 2);
+  REQUIRE(a->getName() == "custom_op_0_IN_0");
+  REQUIRE(outs[1]->getName() == "custom_op_0_OUT_1");
+  REQUIRE(outs[0]->isVirtual());
+  for (auto &o : outs) o->setDim({4, 8}).setStride({8, 1}).setDataType(DataType::Float).setOutput(true);
+  FUSILLI_REQUIRE_OK(g.validate());
+  auto r = g.compileToArtifact(Backend::CUDA, /*remove=*/true);
+  REQUIRE(isError(r));
+  REQUIRE(ErrorObject(r).getCode() == ErrorCode::NotImplemented);
+  REQUIRE(ErrorObject(r).getMessage().find("custom_op_0") != std::string::npos);
+
+  SECTION("missing MLIR") {
+    Graph h;
+    h.setName("custom_bad").setIODataType(DataType::Float).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+    auto x = h.tensor(TensorAttr().setName("x").setDim({4}).setStride({1}));
+    CustomOpAttr bad;
+    bad.setName("op").setNumOutputs(1);
+    h.customOp({x}, bad)[0]->setDim({4}).setStride({1}).setOutput(true);
+    auto st = h.validate();
+    REQUIRE(st.getCode() == ErrorCode::AttributeNotSet);
+    REQUIRE(st.getMessage() == "CustomOp MLIR not set");
+  }
+  SECTION("no outputs") {
+    Graph h;
+    h.setName("custom_bad").setIODataType(DataType::Float).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+    auto x = h.tensor(TensorAttr().setName("x").setDim({4}).setStride({1}));
+    CustomOpAttr bad;
+    bad.setName("op").setMlir("x");
+    h.customOp({x}, bad);
+    auto st = h.validate();
+    REQUIRE(st.getCode() == ErrorCode::AttributeNotSet);
+    REQUIRE(st.getMessage() == "CustomOp outputs not set");
+  }
+}

@@ -36,7 +36,8 @@ void clear_error();
     if (!(cond)) return fb::fail((code), (msg));                               \
   } while (0)
 
-size_t dtype_size(int32_t dtype); // 0 for unsupported types
+size_t dtype_size(int32_t dtype); // 0 for unsupported and for sub-byte types
+size_t dtype_bits(int32_t dtype); // 0 for unsupported types; 4 for Int4 (matmul operands only)
 const char *dtype_name(int32_t dtype);
 
 } // namespace fb
@@ -74,6 +75,7 @@ struct TensorInfo {
   uint32_t dynamic_mask = 0; // bit k: logical dim k takes its extent at execute
   int64_t ws_offset = -1; // >= 0: materialised in the workspace at this byte offset
   int64_t phys_elems() const; // elements of the dense physical buffer
+  size_t phys_bytes() const;  // its size; sub-byte elements are packed, rounded up to a byte
 };
 
 struct NodeInfo {

@@ -64,6 +64,13 @@ __device__ __forceinline__ float load_f(const void *p, int dt, int64_t i) {
   case FB_DT_INT8: return (float)static_cast<const int8_t *>(p)[i];
   case FB_DT_UINT8:
   case FB_DT_BOOLEAN: return (float)static_cast<const uint8_t *>(p)[i];
+  case FB_DT_INT4: {
+    // two's-complement nibbles, element 2k in the low half of byte k (reference
+    // include/fusilli/support/int_types.h:56-66)
+    const uint32_t byte = static_cast<const uint8_t *>(p)[i >> 1];
+    const int v = (int)((byte >> ((i & 1) * 4)) & 0xFu);
+    return (float)((v ^ 8) - 8);
+  }
   default: return 0.f;
   }
 }

@@ -72,9 +72,9 @@ static fb_status check_node(const Plan &p, int ni) {
   case FB_OP_MATMUL:
     for (int id : {d.inputs[0], d.inputs[1], d.outputs[0]}) {
       FB_REQUIRE(id >= 0, FB_INVALID_ARGUMENT, "node '" + nm + "': missing matmul tensor");
-      FB_REQUIRE(is_float_dt(dt(id)), FB_NOT_IMPLEMENTED,
+      FB_REQUIRE(is_float_dt(dt(id)) || (dt(id) == FB_DT_INT4 && id != d.outputs[0]), FB_NOT_IMPLEMENTED,
                  "node '" + nm + "': matmul on " + dtype_name(dt(id)) +
-                     " tensors is not supported (f16, bf16, f32 only)");
+                     " tensors is not supported (f16, bf16, f32; si4 operands)");
     }
     return FB_OK;
   case FB_OP_SDPA:
@@ -126,10 +126,28 @@ static fb_status check_node(const Plan &p, int ni) {
 
 fb_status lower(Plan &p) {
   const int nt = (int)p.tensors.size(), nn = (int)p.nodes.size();
-  for (const TensorInfo &t : p.tensors)
-    FB_REQUIRE(dtype_size(t.dtype) > 0, FB_NOT_IMPLEMENTED,
+  // Int4 exists only as a bound matmul operand (weight-only quantisation, the reference's
+  // samples/matmul/matmul_int4_fp16.cpp); every other use needs byte-addressable elements.
+  std::vector<bool> matmul_operand_only(nt, true), used(nt, false);
+  for (const NodeInfo &n : p.nodes) {
+    for (int k = 0; k < FB_MAX_NODE_INPUTS; ++k) {
+      const int id = n.d.inputs[k];
+      if (id < 0 || id >= nt) continue;
+      used[id] = true;
+      if (n.d.op != FB_OP_MATMUL || k > 1) matmul_operand_only[id] = false;
+    }
+    for (int k = 0; k < FB_MAX_NODE_OUTPUTS; ++k)
+      if (n.d.outputs[k] >= 0 && n.d.outputs[k] < nt) matmul_operand_only[n.d.outputs[k]] = false;
+  }
+  for (int i = 0; i < nt; ++i) {
+    const TensorInfo &t = p.tensors[i];
+    const bool ok = dtype_size(t.dtype) > 0 ||
+                    (t.dtype == FB_DT_INT4 && t.role == FB_TENSOR_INPUT && used[i] && matmul_operand_only[i]);
+    FB_REQUIRE(ok, FB_NOT_IMPLEMENTED,
                "tensor '" + t.name + "': data type " + dtype_name(t.dtype) +
-                   " is not supported by the B200 backend");
+                   (t.dtype == FB_DT_INT4 ? " is supported only as an input operand of a matmul"
+                                          : " is not supported by the B200 backend"));
+  }
   std::vector<int> uses(nt, 0);
   std::vector<std::vector<int>> consumers(nt);
   for (int i = 0; i < nn; ++i) {

@@ -28,9 +28,11 @@ size_t dtype_size(int32_t dt) {
   case FB_DT_UINT8:
   case FB_DT_INT8:
   case FB_DT_BOOLEAN: return 1;
-  default: return 0; // Double, Int4, FP8E5M2: no kernels
+  default: return 0; // Double, FP8E5M2: no kernels; Int4: see dtype_bits
   }
 }
+
+size_t dtype_bits(int32_t dt) { return dt == FB_DT_INT4 ? 4 : dtype_size(dt) * 8; }
 
 const char *dtype_name(int32_t dt) {
   static const char *names[] = {"notset", "f16", "bf16", "f32",  "f64",  "ui8", "si4",
@@ -44,6 +46,8 @@ int64_t TensorInfo::phys_elems() const {
     if (strides[i] != 0) n *= dims[i];
   return n;
 }
+
+size_t TensorInfo::phys_bytes() const { return ((size_t)phys_elems() * dtype_bits(dtype) + 7) / 8; }
 
 void *ExecContext::tensor_ptr(int32_t id) const {
   const TensorInfo &t = plan->tensors[id];
@@ -471,7 +475,7 @@ static fb_status execute_plan(const fb_plan *plan, const Plan &p, fb_device *dev
     FB_REQUIRE(args[a] != nullptr, FB_VARIANT_PACK_ERROR,
                "fb_plan_execute: buffer for tensor '" + t.name + "' is NULL");
     if (arg_bytes) {
-      size_t need = (size_t)t.phys_elems() * dtype_size(t.dtype);
+      size_t need = t.phys_bytes();
       FB_REQUIRE(arg_bytes[a] >= need, FB_INVALID_ARGUMENT,
                  "fb_plan_execute: buffer for tensor '" + t.name + "' has " +
                      std::to_string(arg_bytes[a]) + " bytes, needs " + std::to_string(need));

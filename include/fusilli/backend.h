@@ -96,11 +96,21 @@ public:
                                 ") does not match product of bufferShape dimensions (" +
                                 std::to_string(expected) + ")");
     fb_buffer *b = nullptr;
-    FUSILLI_FB_CALL(fb_buffer_alloc(handle.device(), expected * sizeof(T), &b));
-    Buffer out(b);
-    out.shape_ = bufferShape;
-    FUSILLI_FB_CALL(fb_buffer_h2d(handle.device(), b, bufferData.data(), expected * sizeof(T)));
-    return ok(std::move(out));
+    if constexpr (kIsSubByteElement<T>) {
+      // sub-byte elements travel packed (reference runtime.h:556-560)
+      const std::vector<uint8_t> packed = T::pack(bufferData);
+      FUSILLI_FB_CALL(fb_buffer_alloc(handle.device(), packed.size(), &b));
+      Buffer out(b);
+      out.shape_ = bufferShape;
+      FUSILLI_FB_CALL(fb_buffer_h2d(handle.device(), b, packed.data(), packed.size()));
+      return ok(std::move(out));
+    } else {
+      FUSILLI_FB_CALL(fb_buffer_alloc(handle.device(), expected * sizeof(T), &b));
+      Buffer out(b);
+      out.shape_ = bufferShape;
+      FUSILLI_FB_CALL(fb_buffer_h2d(handle.device(), b, bufferData.data(), expected * sizeof(T)));
+      return ok(std::move(out));
+    }
   }
 
   static ErrorOr<Buffer> allocateRaw(const Handle &handle, size_t sizeInBytes) {
@@ -140,8 +150,20 @@ public:
     FUSILLI_RETURN_ERROR_IF(!outData.empty(), ErrorCode::RuntimeFailure,
                             "Buffer::read failed as outData is NOT empty");
     const size_t bytes = fb_buffer_size(buf_);
-    outData.resize(bytes / sizeof(T));
-    FUSILLI_FB_CALL(fb_buffer_d2h(handle.device(), buf_, outData.data(), outData.size() * sizeof(T)));
+    if constexpr (kIsSubByteElement<T>) {
+      // the element count comes from the shape when there is one, else two per byte
+      std::vector<uint8_t> raw(bytes);
+      FUSILLI_FB_CALL(fb_buffer_d2h(handle.device(), buf_, raw.data(), bytes));
+      size_t count = bytes * 2;
+      if (!shape_.empty()) {
+        count = 1;
+        for (size_t d : shape_) count *= d;
+      }
+      outData = T::unpack(raw.data(), count);
+    } else {
+      outData.resize(bytes / sizeof(T));
+      FUSILLI_FB_CALL(fb_buffer_d2h(handle.device(), buf_, outData.data(), outData.size() * sizeof(T)));
+    }
     return ok();
   }
 

@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <string>
 #include <unordered_map>
+#include <vector>
 
 namespace fusilli {
 
@@ -29,6 +30,41 @@ enum class DataType : uint8_t {
 // Native 16-bit float types, as in the reference on Linux.
 using half = _Float16;
 using bf16 = __bf16;
+
+// Signed 4-bit integer element (reference include/fusilli/support/int_types.h:26-88): values
+// clamp to [-8, 7] on construction; in device buffers two elements share a byte, element 2k in
+// the low half of byte k.
+struct Int4 {
+  static constexpr unsigned kBitWidth = 4;
+  constexpr Int4() = default;
+  Int4(int8_t v) : bits_(static_cast<uint8_t>((v < -8 ? -8 : (v > 7 ? 7 : v)) & 0x0F)) {}
+  [[nodiscard]] constexpr uint8_t toBits() const { return bits_; }
+  [[nodiscard]] constexpr int8_t toInt() const {
+    return static_cast<int8_t>(bits_ & 0x08 ? static_cast<int>(bits_) - 16 : static_cast<int>(bits_));
+  }
+  [[nodiscard]] operator int8_t() const { return toInt(); }
+  [[nodiscard]] static constexpr Int4 fromBits(uint8_t bits) {
+    Int4 r;
+    r.bits_ = bits & 0x0F;
+    return r;
+  }
+  static std::vector<uint8_t> pack(const std::vector<Int4> &elements) {
+    std::vector<uint8_t> bytes((elements.size() + 1) / 2, 0);
+    for (size_t i = 0; i < elements.size(); ++i) bytes[i >> 1] |= static_cast<uint8_t>(elements[i].toBits() << (4 * (i & 1)));
+    return bytes;
+  }
+  static std::vector<Int4> unpack(const uint8_t *bytes, size_t count) {
+    std::vector<Int4> elements(count);
+    for (size_t i = 0; i < count; ++i) elements[i] = fromBits(static_cast<uint8_t>(bytes[i >> 1] >> (4 * (i & 1))));
+    return elements;
+  }
+
+private:
+  uint8_t bits_ = 0;
+};
+using int4 = Int4;
+template <typename T> inline constexpr bool kIsSubByteElement = false;
+template <> inline constexpr bool kIsSubByteElement<Int4> = true;
 
 inline bool isIntegerType(DataType t) {
   switch (t) {
@@ -88,6 +124,7 @@ template <> struct DataTypeOf<int16_t> { static constexpr DataType value = DataT
 template <> struct DataTypeOf<int8_t> { static constexpr DataType value = DataType::Int8; };
 template <> struct DataTypeOf<uint8_t> { static constexpr DataType value = DataType::Uint8; };
 template <> struct DataTypeOf<bool> { static constexpr DataType value = DataType::Boolean; };
+template <> struct DataTypeOf<Int4> { static constexpr DataType value = DataType::Int4; };
 
 } // namespace fusilli
 

@@ -55,6 +55,7 @@ NP_DTYPE = {
     DataType.Double: np.float64, DataType.Uint8: np.uint8, DataType.Int8: np.int8,
     DataType.Int16: np.int16, DataType.Int32: np.int32, DataType.Int64: np.int64,
     DataType.Boolean: np.uint8,
+    DataType.Int4: np.uint8,  # packed: element 2k in the low half of byte k (int_types.h:56-66)
 }
 _FLOAT_TYPES = (DataType.Half, DataType.BFloat16, DataType.Float, DataType.Double)
 
@@ -72,12 +73,33 @@ def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
     return (b.astype(np.uint32) << 16).view(np.float32)
 
 
+def pack_int4(values: np.ndarray) -> np.ndarray:
+    """Signed 4-bit elements (clamped to [-8, 7]) -> packed bytes, element 2k in the low half of
+    byte k (reference include/fusilli/support/int_types.h:32-66)."""
+    v = np.clip(np.asarray(values).astype(np.int64).reshape(-1), -8, 7).astype(np.uint8) & 0x0F
+    if v.size % 2:
+        v = np.concatenate([v, np.zeros(1, np.uint8)])
+    return (v[0::2] | (v[1::2] << 4)).astype(np.uint8)
+
+
+def unpack_int4(raw: np.ndarray, count: int) -> np.ndarray:
+    """Packed bytes -> int8 values with sign extension from bit 3 (int_types.h:37-41, 69-78)."""
+    b = np.asarray(raw, dtype=np.uint8).reshape(-1)
+    nib = np.empty(b.size * 2, np.uint8)
+    nib[0::2] = b & 0x0F
+    nib[1::2] = b >> 4
+    v = nib[:count].astype(np.int8)
+    return np.where(v >= 8, v - 16, v).astype(np.int8)
+
+
 def to_storage(values: np.ndarray, dtype: DataType) -> np.ndarray:
     """Rounds a float / int array to ``dtype``'s storage representation."""
     if dtype == DataType.BFloat16:
         return f32_to_bf16_bits(values.astype(np.float32))
     if dtype == DataType.Boolean:
         return (values != 0).astype(np.uint8)
+    if dtype == DataType.Int4:
+        return pack_int4(values)
     return values.astype(NP_DTYPE[dtype])
 
 
@@ -246,7 +268,11 @@ def execute(graph: GraphBase, inputs: Dict[TensorAttr, np.ndarray]) -> Dict[Tens
             arr = np.array([v], dtype=np.float32 if t.dataType in _FLOAT_TYPES else np.int64)
         else:
             flat = np.ascontiguousarray(inputs[t]).reshape(-1)
-            arr = from_storage(logical_view(flat, t), t.dataType)
+            if t.dataType == DataType.Int4:
+                # only ever a matmul operand: unpack, then compute in float (values are exact)
+                arr = logical_view(unpack_int4(flat, t.physicalVolume()), t).astype(np.float32)
+            else:
+                arr = from_storage(logical_view(flat, t), t.dataType)
         vals[id(t)] = arr
         return arr
 

@@ -30,7 +30,7 @@ OWN_SOURCES = ["test_frontend_host.cpp", "test_frontend_device.cpp"]
 
 # Reference programs that only need the graph API of the operators in scope. Paths are relative
 # to the reference checkout. SDPA samples there go through a user-supplied MLIR custom op and
-# batchnorm / int4 / custom ops are outside this backend, so they are not listed. Of the dynamic-shape
+# batchnorm / custom ops are outside this backend, so they are not listed. Of the dynamic-shape
 # samples, the reduction one is an expected failure in the reference itself (it requires the
 # IREE-specific non-zero transient size) and the custom-op one needs MLIR.
 REFERENCE_SAMPLES = [
@@ -51,6 +51,7 @@ REFERENCE_SAMPLES = [
     "samples/matmul/matmul_basic_with_bias.cpp",
     "samples/matmul/matmul_batched.cpp",
     "samples/matmul/matmul_batched_with_bias.cpp",
+    "samples/matmul/matmul_int4_fp16.cpp",
     "samples/pointwise/pointwise_add_transposed.cpp",
     "samples/pointwise/pointwise_binary_cmp_ops.cpp",
     "samples/pointwise/pointwise_binary_ops.cpp",
@@ -109,12 +110,13 @@ REFERENCE_HOST_TESTS = [
     "tests/test_reduction_node.cpp",
     "tests/test_pointwise_attributes.cpp",
     "tests/test_pointwise_node.cpp",
+    "tests/test_int_types.cpp",
 ]
 # Not listed, because they exercise parts this backend does not have: test_graph (MLIR emission and
 # the IREE compile cache), test_handle / test_buffer / test_utils (CPU and AMDGPU HAL devices),
 # test_compile_*, test_dllib, test_process, test_memstream, test_extras, test_logging (compiler
-# driver plumbing), test_float_types / test_int_types (software float and int4 types), batchnorm
-# and custom ops.
+# driver plumbing), test_float_types (software float types; half and bf16 are the compiler's native
+# types here), batchnorm and custom ops.
 
 
 def _flags():

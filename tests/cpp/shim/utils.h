@@ -75,6 +75,7 @@ inline ErrorOr<std::shared_ptr<Buffer>> allocateBufferOfType(Handle &handle, con
   case DataType::Int8:
   case DataType::Boolean: return allocateBufferOfType(handle, tensor, std::vector<int8_t>(n, int8_t(initVal)));
   case DataType::Uint8: return allocateBufferOfType(handle, tensor, std::vector<uint8_t>(n, uint8_t(initVal)));
+  case DataType::Int4: return allocateBufferOfType(handle, tensor, std::vector<int4>(n, int4(int8_t(initVal))));
   default: return error(ErrorCode::InvalidAttribute, "Unsupported DataType");
   }
 }

@@ -43,6 +43,8 @@ def make_input(t: TensorAttr, rng: np.random.Generator, dist=("uniform", -1.0, 1
         return orc.to_storage(vals, t.dataType)
     if t.dataType == DataType.Boolean:
         return rng.integers(0, 2, n).astype(np.uint8)
+    if t.dataType == DataType.Int4:
+        return orc.pack_int4(rng.integers(-8, 8, n))
     if dist[0] == "const":
         return np.full(n, int(dist[1]), orc.NP_DTYPE[t.dataType])
     return rng.integers(-50, 50, n).astype(orc.NP_DTYPE[t.dataType])
@@ -60,7 +62,7 @@ def run_gpu(graph: fz.Graph, inputs: Dict[TensorAttr, np.ndarray], handle: Optio
     pack = {}
     outs = {}
     for t, arr in inputs.items():
-        pack[t] = fz.Buffer.allocate(handle, [arr.size], arr)
+        pack[t] = fz.Buffer.allocate(handle, [arr.size], arr)  # Int4 arrives packed: bytes, not elements
     for t in graph.outputs:
         if t.isVirtual():
             continue

@@ -135,6 +135,21 @@ def matmul_transposed_b_f16():
     return g, {a: _fill(a, 1.0), bt: _fill(bt, 1.0)}, lambda o: np.all(o[c] == np.float16(k))
 
 
+def matmul_int4_fp16():
+    """samples/matmul/matmul_int4_fp16.cpp:30-98: A si4 ones (packed nibbles), B f16 ones -> k."""
+    b, m, k, n = 1, 4, 8, 4
+    g = fz.Graph()
+    g.setName("kat_matmul_int4").setIODataType(F16).setComputeDataType(F32).setIntermediateDataType(F32)
+    a = g.tensor(TensorAttr().setName("a").setDim([b, m, k]).setStride([m * k, k, 1]).setDataType(DataType.Int4))
+    bt = g.tensor(TensorAttr().setName("b").setDim([b, k, n]).setStride([k * n, n, 1]))
+    c = g.matmul(a, bt, fz.MatmulAttr().setName("matmul"))
+    c.setName("c").setOutput(True)
+    g.validate()
+    ones = orc.pack_int4(np.ones(b * m * k))
+    assert ones.size == b * m * k // 2 and np.all(ones == 0x11)
+    return g, {a: ones, bt: _fill(bt, 1.0)}, lambda o: np.all(o[c] == np.float16(k))
+
+
 def _sdpa_case(name, causal=False, mask=False, hk=8, hv=8, sq=64, skv=64):
     """samples/sdpa/*.cpp against samples/sdpa_utils.cpp:49-102 (constant fills 0.01):
     softmax over equal scores is uniform, so every output element equals the V fill."""
@@ -268,6 +283,7 @@ CASES = {
     "conv_wgrad_grouped_strided": conv_wgrad_grouped_strided,
     "matmul_batched_bias": matmul_batched_bias,
     "matmul_transposed_b_f16": matmul_transposed_b_f16,
+    "matmul_int4_fp16": matmul_int4_fp16,
     "sdpa_mha": lambda: _sdpa_case("kat_sdpa_mha"),
     "sdpa_causal": lambda: _sdpa_case("kat_sdpa_causal", causal=True),
     "sdpa_mask": lambda: _sdpa_case("kat_sdpa_mask", mask=True),

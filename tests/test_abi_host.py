@@ -209,3 +209,44 @@ def test_tensor_layout_algebra():
     assert not TensorAttr().setDim([2, 3]).setStride([4, 1]).hasValidPhysicalRepresentation()
     assert fz.graph.computeBroadcastShape([[64, 16, 1, 1], [1, 32, 1]]) == [64, 16, 32, 1]
     assert fz.graph.getConvInferredOutputShape([16, 64, 56, 56], [64, 64, 3, 3], [1, 1], [1, 1], [1, 1]) == [16, 64, 56, 56]
+
+
+def _int4_graph(as_pointwise_input=False, as_output=False):
+    g = fz.Graph()
+    g.setName("int4_host").setIODataType(DataType.Half).setComputeDataType(DataType.Float)
+    g.setIntermediateDataType(DataType.Float)
+    a = g.tensor(TensorAttr().setName("a").setDim([1, 4, 8]).setStride([32, 8, 1]).setDataType(DataType.Int4))
+    if as_pointwise_input:
+        o = g.pointwise(a, fz.PointwiseAttr().setMode(PointwiseMode.RELU_FWD))
+    else:
+        b = g.tensor(TensorAttr().setName("b").setDim([1, 8, 4]).setStride([32, 4, 1]))
+        o = g.matmul(a, b, fz.MatmulAttr().setName("mm"))
+    o.setName("o").setOutput(True)
+    if as_output:
+        o.setDataType(DataType.Int4)
+    g.validate()
+    return g
+
+
+def test_int4_is_a_matmul_operand_and_nothing_else():
+    """Int4 x f16 matmul builds a plan (reference samples/matmul/matmul_int4_fp16.cpp); every other
+    use of the sub-byte type is refused when the plan is built."""
+    blob = _int4_graph().compileToArtifact()
+    assert runtime.lib().fb_plan_check(blob, len(blob)) == 0
+    for kwargs in (dict(as_pointwise_input=True), dict(as_output=True)):
+        with pytest.raises(FusilliError) as e:
+            _int4_graph(**kwargs).compileToArtifact()
+        assert e.value.code == ErrorCode.NotImplemented
+        assert "si4" in e.value.message
+
+
+def test_mixed_precision_matmul_needs_rank_3_and_equal_batch():
+    g = fz.Graph()
+    g.setName("int4_rank2").setIODataType(DataType.Half).setComputeDataType(DataType.Float)
+    a = g.tensor(TensorAttr().setName("a").setDim([4, 8]).setStride([8, 1]).setDataType(DataType.Int4))
+    b = g.tensor(TensorAttr().setName("b").setDim([8, 4]).setStride([4, 1]))
+    g.matmul(a, b, fz.MatmulAttr().setName("mm")).setOutput(True)
+    with pytest.raises(FusilliError) as e:
+        g.validate()
+    assert e.value.code == ErrorCode.InvalidAttribute
+    assert "Mixed precision matmul is only supported when input tensors A and B are of rank 3" in e.value.message

@@ -165,6 +165,40 @@ def test_matmul_batch_broadcast_and_transposed_a():
     check_graph(g, _inputs({"a": a, "b": b}, 12), scale_atol=4.0)
 
 
+def _int4_matmul(b, m, k, n, other, a_int4=True, bias=False, odd_k=False):
+    """si4 x f16/bf16 matmul (the reference's samples/matmul/matmul_int4_fp16.cpp pattern); mixed
+    element types need rank 3 with equal batch (matmul_node.h:155-177)."""
+    g = fz.Graph()
+    g.setName("mm_int4").setIODataType(other).setComputeDataType(F32).setIntermediateDataType(F32)
+    a = g.tensor(TensorAttr().setName("a").setDim([b, m, k]).setStride(contiguousStride([b, m, k])))
+    bt = g.tensor(TensorAttr().setName("b").setDim([b, k, n]).setStride(contiguousStride([b, k, n])))
+    (a if a_int4 else bt).setDataType(DataType.Int4)
+    c = g.matmul(a, bt, fz.MatmulAttr().setName("mm"))
+    ins = {"a": a, "b": bt}
+    if bias:
+        bi = g.tensor(TensorAttr().setName("bias").setDim([1, 1, n]).setStride([n, n, 1]))
+        c = g.pointwise(c, bi, fz.PointwiseAttr().setMode(PointwiseMode.ADD).setName("bias_add"))
+        ins["bias"] = bi
+    c.setName("c").setOutput(True)
+    g.validate()
+    return g, ins
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(b=1, m=4, k=8, n=4, other=F16),                       # the reference sample's shape
+    dict(b=3, m=33, k=96, n=40, other=F16, bias=True),
+    dict(b=2, m=17, k=63, n=25, other=BF16),                   # odd K: rows start in the middle of a byte
+    dict(b=2, m=24, k=64, n=31, other=F16, a_int4=False),      # quantised B, odd N
+    dict(b=1, m=128, k=512, n=256, other=BF16, bias=True),     # large enough for tensor cores, stays on CUDA cores
+])
+def test_matmul_int4_operand(cfg):
+    g, ins = _int4_matmul(**cfg)
+    data = _inputs(ins, 21, ("normal", 0.0, 0.5))
+    check_graph(g, data, scale_atol=8.0)
+    assert g.numLaunches() == 1
+    assert "gemm_tcgen05" not in g.statistics()
+
+
 # ---- sdpa ---------------------------------------------------------------------------
 @pytest.mark.parametrize("cfg", [
     dict(b=1, h=8, s=64, d=64, dtype=F16, causal=False),

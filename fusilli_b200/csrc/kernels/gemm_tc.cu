@@ -3,7 +3,7 @@
 //
 // Persistent, warp-specialised, one CTA per SM:
 //   warp 0      TMA producer: per 64-wide K block one A tile (128 x 64) and one B
-//               tile (64 x 256) land in a 4-stage ring of 128B-swizzled shared memory
+//               tile (64 x 256, or 64 x 128 for a half tile) land in a 4-stage ring of 128B-swizzled shared memory
 //               (cp.async.bulk.tensor, no multicast, zero fill past the edges).
 //   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16 (cta_group::1),
 //               four per K block, accumulating into one of two 256-column TMEM
@@ -42,11 +42,33 @@ struct GemmTcParams {
   int32_t a_batch_mul, b_batch_mul;
   int32_t ab_format;
   int32_t tiles_m, tiles_n, total_tiles;
+  // Work items: tiles [0, full_tiles) whole, the rest as two 128-column halves each. The host
+  // splits the tiles of a last, less than half full wave, which then takes half a tile's time.
+  int32_t full_tiles, total_work;
   void *out;
   int64_t ldc, c_bstride;
   uint32_t *err;
   TcEpilogue epi;
 };
+
+struct WorkItem {
+  int m0, n0, b, nb; // output origin, batch, columns of this item (BN or BN / 2)
+};
+__device__ __forceinline__ WorkItem decode_work(const GemmTcParams &p, int w) {
+  int tile = w, n_off = 0, nb = BN;
+  if (w >= p.full_tiles) {
+    const int r = w - p.full_tiles;
+    tile = p.full_tiles + (r >> 1);
+    n_off = (r & 1) * (BN / 2);
+    nb = BN / 2;
+  }
+  WorkItem it;
+  it.m0 = (tile % p.tiles_m) * BM;
+  it.n0 = ((tile / p.tiles_m) % p.tiles_n) * BN + n_off;
+  it.b = tile / (p.tiles_m * p.tiles_n);
+  it.nb = nb;
+  return it;
+}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -90,16 +112,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % p.tiles_m;
-        const int tn = (tile / p.tiles_m) % p.tiles_n;
-        const int b = tile / (p.tiles_m * p.tiles_n);
-        const int m0 = tm * BM, n0 = tn * BN;
+      for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
+        const WorkItem wi = decode_work(p, w);
+        const int m0 = wi.m0, n0 = wi.n0, b = wi.b, nb = wi.nb;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          mbar_expect_tx(full_bar(s), A_BYTES + nb * BK * 2);
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
           const int k0 = kb * BK;
           if (!p.a_mn_major) {
@@ -110,11 +130,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               tma_load_3d(sa + i * (64 * BK * 2), &tmap_a, full_bar(s), m0 + 64 * i, k0, b * p.a_batch_mul);
           }
           if (!p.b_mn_major) {
-            tma_load_3d(sb, &tmap_b, full_bar(s), k0, n0, b * p.b_batch_mul);
+            // boxes of BN / 2 rows: one per half
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              if (i * (BN / 2) < nb)
+                tma_load_3d(sb + i * ((BN / 2) * BK * 2), &tmap_b, full_bar(s), k0, n0 + (BN / 2) * i, b * p.b_batch_mul);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i)
-              tma_load_3d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), n0 + 64 * i, k0, b * p.b_batch_mul);
+              if (i * 64 < nb)
+                tma_load_3d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), n0 + 64 * i, k0, b * p.b_batch_mul);
           }
         }
       }
@@ -123,7 +148,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
     // elected lane issues the MMAs and the commits, which track the issuing thread.
     const bool leader = elect_one();
-    const uint32_t idesc = make_idesc_f16(BM, BN, p.ab_format, p.a_mn_major, p.b_mn_major);
+    const uint32_t idesc_full = make_idesc_f16(BM, BN, p.ab_format, p.a_mn_major, p.b_mn_major);
+    const uint32_t idesc_half = make_idesc_f16(BM, BN / 2, p.ab_format, p.a_mn_major, p.b_mn_major);
     // K-major: rows of 128 B, 8-row groups 1024 B apart; a 16-element K step is 32 B.
     // MN-major: 64-element MN blocks 8 KB apart (LBO), 8-row K groups 1024 B apart;
     // a 16-element K step is two K groups = 2048 B.
@@ -134,7 +160,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint64_t b_desc0 = make_smem_desc(smem_base + A_BYTES, b_lbo, 1024);
     uint32_t it = 0, lt = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++lt) {
+      const uint32_t idesc = w < p.full_tiles ? idesc_full : idesc_half;
       const int acc = lt & 1;
       const uint32_t aph = (lt >> 1) & 1;
       if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
@@ -160,24 +187,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int q = warp & 3; // TMEM lane quadrant this warp may access
     uint32_t lt = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
-      const int tm = tile % p.tiles_m;
-      const int tn = (tile / p.tiles_m) % p.tiles_n;
-      const int b = tile / (p.tiles_m * p.tiles_n);
+    for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x, ++lt) {
+      const WorkItem wi = decode_work(p, w);
+      const int b = wi.b, chunks = wi.nb / 32;
       const int acc = lt & 1;
       const uint32_t aph = (lt >> 1) & 1;
       if (!mbar_wait(tfull_bar(acc), aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int m = tm * BM + q * 32 + lane;
-      const int n0 = tn * BN;
+      const int m = wi.m0 + q * 32 + lane;
+      const int n0 = wi.n0;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const int64_t row_off = (int64_t)b * p.c_bstride + (int64_t)m * p.ldc;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < chunks; ++c) {
         uint32_t raw[32];
         tmem_ld_32x32(taddr + c * 32, raw);
         tmem_ld_wait();
-        if (c == BN / 32 - 1) {
+        if (c == chunks - 1) {
           // all of this warp's reads of the accumulator are done: hand it back
           tc_fence_before();
           __syncwarp();
@@ -380,6 +406,14 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.batches;
   FB_REQUIRE(total < (1ll << 31), FB_NOT_IMPLEMENTED, "gemm_tcgen05: too many tiles");
   p.total_tiles = (int)total;
+  {
+    // A last wave that fills at most half of the SMs runs as half tiles on twice as many SMs.
+    const int sms = cx.dev->sm_count;
+    const int tail = p.total_tiles % sms;
+    const bool split = tail > 0 && 2 * tail <= sms && p.N > BN / 2;
+    p.full_tiles = split ? p.total_tiles - tail : p.total_tiles;
+    p.total_work = p.full_tiles + 2 * (p.total_tiles - p.full_tiles);
+  }
   p.out = cptr;
   p.ldc = g.ldc;
   p.c_bstride = g.c_bs;
@@ -424,7 +458,7 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
     }
     if (!g.b_mn) {
       uint64_t dims[3] = {(uint64_t)g.K, (uint64_t)g.N, bb}, str[2] = {(uint64_t)g.b_ld * 2, b_bstride};
-      uint32_t box[3] = {BK, BN, 1};
+      uint32_t box[3] = {BK, BN / 2, 1};
       FB_REQUIRE(encode_tmap_2byte(&tmB, bptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
     } else {
       uint64_t dims[3] = {(uint64_t)g.N, (uint64_t)g.K, bb}, str[2] = {(uint64_t)g.b_ld * 2, b_bstride};
@@ -439,7 +473,7 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   FB_REQUIRE(attr_err == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("gemm_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
   (void)attr_once;
-  int grid = std::min<int>(p.total_tiles, cx.dev->sm_count);
+  int grid = std::min<int>(p.total_work, cx.dev->sm_count);
   gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
   return FB_OK;
 }

@@ -76,6 +76,19 @@ static fb_status check_node(const Plan &p, int ni) {
                  "node '" + nm + "': matmul on " + dtype_name(dt(id)) +
                      " tensors is not supported (f16, bf16, f32; si4 operands)");
     }
+    {
+      // The reference lets a batch dim of one operand divide the other's (matmul_node.h:140-150);
+      // the kernels broadcast a batch dim only from 1, and say so here rather than at execute.
+      const TensorInfo &a = p.tensors[d.inputs[0]], &b = p.tensors[d.inputs[1]], &c = p.tensors[d.outputs[0]];
+      FB_REQUIRE(a.rank >= 2 && a.rank == b.rank && a.rank == c.rank, FB_INVALID_ARGUMENT,
+                 "node '" + nm + "': matmul tensors must have one rank >= 2");
+      FB_REQUIRE(a.rank - 2 <= 6, FB_NOT_IMPLEMENTED, "node '" + nm + "': more than 6 matmul batch dims");
+      for (int i = 0; i + 2 < a.rank; ++i)
+        FB_REQUIRE((a.dims[i] == c.dims[i] || a.dims[i] == 1) && (b.dims[i] == c.dims[i] || b.dims[i] == 1),
+                   FB_NOT_IMPLEMENTED,
+                   "node '" + nm + "': matmul batch dim " + std::to_string(i) +
+                       " broadcasts by a proper divisor, which is not supported");
+    }
     return FB_OK;
   case FB_OP_SDPA:
     for (int id : {d.inputs[0], d.inputs[1], d.inputs[2], d.outputs[0]}) {

@@ -250,3 +250,19 @@ def test_mixed_precision_matmul_needs_rank_3_and_equal_batch():
         g.validate()
     assert e.value.code == ErrorCode.InvalidAttribute
     assert "Mixed precision matmul is only supported when input tensors A and B are of rank 3" in e.value.message
+
+
+def test_matmul_batch_broadcast_by_a_divisor_is_refused_at_plan_build():
+    """The reference's validation lets a batch dim divide the other operand's (matmul_node.h:140-150);
+    the kernels broadcast from 1 only, and the refusal comes from the plan build, not from execute."""
+    g = fz.Graph()
+    g.setName("mm_divisor").setIODataType(DataType.Float).setComputeDataType(DataType.Float)
+    g.setIntermediateDataType(DataType.Float)
+    a = g.tensor(TensorAttr().setName("a").setDim([4, 8, 16]).setStride([128, 16, 1]))
+    b = g.tensor(TensorAttr().setName("b").setDim([2, 16, 8]).setStride([128, 8, 1]))
+    g.matmul(a, b, fz.MatmulAttr().setName("mm")).setName("c").setOutput(True)
+    g.validate()
+    with pytest.raises(FusilliError) as e:
+        g.compileToArtifact()
+    assert e.value.code == ErrorCode.NotImplemented
+    assert "proper divisor" in e.value.message

@@ -139,6 +139,9 @@ def test_conv_fprop_f32_channels_last(geom):
     (1, 128, 64, 32, BF16, False, False),    # smallest shape the tensor-core kernel takes
     (2, 96, 80, 72, F32, True, False),       # fp32: CUDA-core kernel
     (4, 16, 32, 64, F16, True, False),       # tiny: CUDA-core kernel
+    (1, 2048, 2560, 128, BF16, True, False),  # 160 tiles on 148 SMs: whole tiles, then 12 split into halves
+    (1, 2048, 2560, 128, F16, False, True),   # the same with a K-major B (two 128-row boxes per tile)
+    (1, 1024, 1152, 192, BF16, True, False),  # 40 tiles, all split; the last column tile has one half out of range
 ])
 def test_matmul(cfg):
     b, m, n, k, dtype, bias, trans_b = cfg

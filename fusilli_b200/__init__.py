@@ -5,12 +5,12 @@ Python surface = the reference's C++ surface with the same names
 in libfusilli_b200.so through the C ABI declared in include/fusilli_b200.h.
 """
 from .graph import (ConvDGradAttr, ConvFPropAttr, ConvWGradAttr, DataType, ErrorCode, FusilliError,
-                    LayernormAttr, MatmulAttr, NormFwdPhase, PointwiseAttr, ReductionAttr, RmsnormAttr,
+                    BatchnormAttr, LayernormAttr, MatmulAttr, NormFwdPhase, PointwiseAttr, ReductionAttr, RmsnormAttr,
                     SdpaAttr, TensorAttr, channelsLastStride, contiguousStride)
 from .runtime import Backend, Buffer, Graph, Handle
 
 __all__ = [
     "Backend", "Buffer", "ConvDGradAttr", "ConvFPropAttr", "ConvWGradAttr", "DataType", "ErrorCode",
-    "FusilliError", "Graph", "Handle", "LayernormAttr", "MatmulAttr", "NormFwdPhase", "PointwiseAttr",
+    "BatchnormAttr", "FusilliError", "Graph", "Handle", "LayernormAttr", "MatmulAttr", "NormFwdPhase", "PointwiseAttr",
     "ReductionAttr", "RmsnormAttr", "SdpaAttr", "TensorAttr", "channelsLastStride", "contiguousStride",
 ]

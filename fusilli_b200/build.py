@@ -18,6 +18,7 @@ SOURCES = [
     "kernels/pointwise.cu",
     "kernels/reduce.cu",
     "kernels/norm.cu",
+    "kernels/batchnorm.cu",
     "kernels/contract_simt.cu",
     "kernels/sdpa_simt.cu",
     "kernels/gemm_tc.cu",

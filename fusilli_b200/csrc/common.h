@@ -89,6 +89,7 @@ enum StepKind : int32_t {
   STEP_NORM = 3,      // layernorm / rmsnorm
   STEP_CONTRACT = 4,  // conv fprop/dgrad/wgrad or matmul (+ fused epilogue)
   STEP_SDPA = 5,
+  STEP_BATCHNORM = 6, // training: partial statistics, merge, apply; inference: apply
 };
 
 enum Engine : int32_t {
@@ -166,6 +167,9 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s);
 fb_status launch_conv_tc(const ExecContext &cx, const Step &s);
 fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s);
 fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s);
+fb_status launch_batchnorm(const ExecContext &cx, const Step &s);
+// Workspace the batch-statistics pass needs (0 in inference); *splits = slices of the reduction.
+int64_t batchnorm_scratch_bytes(const Plan &p, const Step &s, int32_t *splits);
 
 // Eligibility checks used by the lowering (pure host logic, no device).
 bool gemm_tc_eligible(const Plan &p, const Step &s);

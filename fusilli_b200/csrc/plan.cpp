@@ -115,6 +115,27 @@ static fb_status check_node(const Plan &p, int ni) {
                "RmsNorm training forward phase is not implemented");
     return FB_OK;
   }
+  case FB_OP_BATCHNORM: {
+    FB_REQUIRE(d.inputs[0] >= 0 && d.outputs[0] >= 0, FB_INVALID_ARGUMENT, "node '" + nm + "': missing X or Y");
+    FB_REQUIRE(d.inputs[5] >= 0 && p.tensors[d.inputs[5]].role == FB_TENSOR_SCALAR, FB_INVALID_ARGUMENT,
+               "node '" + nm + "': epsilon must be a scalar constant");
+    const TensorInfo &x = p.tensors[d.inputs[0]];
+    FB_REQUIRE(x.rank >= 2 && same_dims(x, p.tensors[d.outputs[0]]), FB_INVALID_ARGUMENT,
+               "node '" + nm + "': X and Y must have one shape of rank >= 2");
+    for (int id : {d.inputs[0], d.inputs[1], d.inputs[2], d.inputs[3], d.inputs[4], d.outputs[0], d.outputs[1],
+                   d.outputs[2]}) {
+      if (id < 0) continue;
+      FB_REQUIRE(is_float_dt(dt(id)), FB_NOT_IMPLEMENTED,
+                 "node '" + nm + "': batch normalisation tensors must be f16, bf16 or f32");
+      if (id != d.inputs[0] && id != d.outputs[0])
+        FB_REQUIRE(p.tensors[id].rank == 1 && p.tensors[id].dims[0] == x.dims[1] && p.tensors[id].strides[0] == 1,
+                   FB_INVALID_ARGUMENT, "node '" + nm + "': per-channel tensors must be dense [C]");
+    }
+    if (!(d.flags & FB_FLAG_NORM_TRAINING))
+      FB_REQUIRE(d.inputs[3] >= 0 && d.inputs[4] >= 0, FB_INVALID_ARGUMENT,
+                 "node '" + nm + "': inference needs the running MEAN and VAR");
+    return FB_OK;
+  }
   case FB_OP_REDUCTION:
     FB_REQUIRE(d.mode > FB_RED_NOT_SET && d.mode < FB_RED_MODE_COUNT, FB_INVALID_ARGUMENT,
                "node '" + nm + "': bad reduction mode");
@@ -257,6 +278,10 @@ fb_status lower(Plan &p) {
       break;
     case FB_OP_LAYERNORM:
     case FB_OP_RMSNORM: s.kind = STEP_NORM; break;
+    case FB_OP_BATCHNORM:
+      s.kind = STEP_BATCHNORM;
+      s.scratch_bytes = batchnorm_scratch_bytes(p, s, &s.split_k);
+      break;
     case FB_OP_REDUCTION: s.kind = STEP_REDUCTION; break;
     case FB_OP_POINTWISE: s.kind = STEP_POINTWISE; break;
     default: return fail(FB_INTERNAL_ERROR, "lower: unexpected op");
@@ -276,7 +301,7 @@ fb_status lower(Plan &p) {
   for (Step &s : p.steps) {
     place(s.out_tensor);
     const fb_node_desc &d = p.nodes[s.node].d;
-    if (s.kind == STEP_NORM)
+    if (s.kind == STEP_NORM || s.kind == STEP_BATCHNORM)
       for (int k = 1; k < FB_MAX_NODE_OUTPUTS; ++k)
         if (d.outputs[k] >= 0 && uses[d.outputs[k]] > 0) place(d.outputs[k]);
     if (s.scratch_bytes > 0) {
@@ -341,6 +366,7 @@ static int64_t implied_out_dim(const Plan &p, const fb_node_desc &d, int slot, i
   case FB_OP_RMSNORM:
     if (slot == 0 || k == 0) return T(d.inputs[0]).dims[k];
     return 1;
+  case FB_OP_BATCHNORM: return slot == 0 ? T(d.inputs[0]).dims[k] : T(d.inputs[0]).dims[1];
   case FB_OP_REDUCTION: return T(d.inputs[0]).dims[k]; // a dynamic dim is never a reduced one
   case FB_OP_POINTWISE: {
     const int r = T(d.outputs[0]).rank;
@@ -623,6 +649,7 @@ const char *step_kernel_name(const Plan &p, const Step &s) {
   case STEP_POINTWISE: return "pointwise";
   case STEP_REDUCTION: return "reduction";
   case STEP_NORM: return op == FB_OP_LAYERNORM ? "layernorm" : "rmsnorm";
+  case STEP_BATCHNORM: return "batchnorm";
   case STEP_SDPA: return tc ? "sdpa_fwd_tcgen05" : "sdpa_fwd_simt";
   case STEP_CONTRACT:
     switch (op) {
@@ -636,6 +663,7 @@ const char *step_kernel_name(const Plan &p, const Step &s) {
 }
 
 int step_launches(const Plan &p, const Step &s) {
+  if (s.kind == STEP_BATCHNORM) return (p.nodes[s.node].d.flags & FB_FLAG_NORM_TRAINING) ? 3 : 1;
   const bool wgrad = p.nodes[s.node].d.op == FB_OP_CONV_WGRAD;
   if (wgrad && s.engine == ENGINE_TCGEN05) return 2; // partial kernel + slice reduction
   return s.split_k > 1 ? 2 : 1;

@@ -497,6 +497,7 @@ static fb_status execute_plan(const fb_plan *plan, const Plan &p, fb_device *dev
     case STEP_POINTWISE: st = launch_pointwise(cx, s); break;
     case STEP_REDUCTION: st = launch_reduction(cx, s); break;
     case STEP_NORM: st = launch_norm(cx, s); break;
+    case STEP_BATCHNORM: st = launch_batchnorm(cx, s); break;
     case STEP_CONTRACT:
       if (s.engine == ENGINE_TCGEN05) {
         const int op = p.nodes[s.node].d.op;

@@ -92,6 +92,7 @@ class Op(enum.IntEnum):
     RMSNORM = 7
     REDUCTION = 8
     POINTWISE = 9
+    BATCHNORM = 10
 
 
 _PW_NAMES = (
@@ -369,6 +370,17 @@ class LayernormAttr(_NormAttr): pass
 class RmsnormAttr(_NormAttr): pass
 
 
+class BatchnormAttr(_NormAttr):
+    """attributes/batchnorm_attributes.h:27-90: epsilon and momentum are scalar tensors."""
+
+    def __init__(self):
+        super().__init__()
+        self.momentum: Optional[TensorAttr] = None
+
+    def setMomentum(self, m): self.momentum = m; return self
+    def getMomentum(self): return self.momentum
+
+
 class ReductionAttr(_Attr):
     Mode = ReductionMode
 
@@ -509,6 +521,19 @@ class GraphBase:
             v = self._out(attr.name + "_INV_VARIANCE")
         self.nodes.append(Node(Op.LAYERNORM, attr, [x, scale, bias, attr.epsilon], [y, m, v]))
         return y, m, v
+
+    def batchnorm(self, x, scale, bias, mean, var, attr: BatchnormAttr):
+        """graph.h:857-912: Y always; SAVED_MEAN and SAVED_INV_VARIANCE in the training phase."""
+        self._auto(attr, "batchnorm", {"X": x, "SCALE": scale, "BIAS": bias, "MEAN": mean, "VAR": var,
+                                       "EPSILON": attr.epsilon, "MOMENTUM": attr.momentum})
+        y = self._out(attr.name + "_Y")
+        sm = si = None
+        if attr.forwardPhase == NormFwdPhase.TRAINING:
+            sm = self._out(attr.name + "_SAVED_MEAN")
+            si = self._out(attr.name + "_SAVED_INV_VARIANCE")
+        self.nodes.append(Node(Op.BATCHNORM, attr, [x, scale, bias, mean, var, attr.epsilon, attr.momentum],
+                               [y, sm, si]))
+        return y, sm, si
 
     def rmsnorm(self, x, scale, attr: RmsnormAttr):
         self._auto(attr, "rmsnorm", {"X": x, "SCALE": scale, "EPSILON": attr.epsilon})
@@ -876,6 +901,56 @@ def _v_pointwise(g: GraphBase, n: Node):
                  "Pointwise output strides could not be computed")
 
 
+def _v_batchnorm(g: GraphBase, n: Node):
+    """node/batchnorm_node.h:52-236."""
+    a: BatchnormAttr = n.attr
+    x, scale, bias, mean, var = n.inputs[:5]
+    y, sm, si = n.outputs
+    training = a.forwardPhase == NormFwdPhase.TRAINING
+    _require(a.forwardPhase != NormFwdPhase.NOT_SET, ErrorCode.AttributeNotSet, "BatchNorm forward phase not set")
+    _require(x is not None, ErrorCode.AttributeNotSet, "BatchNorm input tensor X not set")
+    _require(y is not None, ErrorCode.AttributeNotSet, "BatchNorm output tensor Y not set")
+    _require(len(x.dim) >= 2, ErrorCode.InvalidAttribute, "BatchNorm input tensor X must have a rank of at least 2")
+    _require(_layout_ok(x), ErrorCode.NotImplemented, _not_cl(x))
+    if not training:
+        _require(mean is not None, ErrorCode.AttributeNotSet, "BatchNorm inference requires running MEAN")
+        _require(var is not None, ErrorCode.AttributeNotSet, "BatchNorm inference requires running VAR")
+        _require(sm is None, ErrorCode.InvalidAttribute, "BatchNorm SAVED_MEAN should not be set in inference mode")
+        _require(si is None, ErrorCode.InvalidAttribute,
+                 "BatchNorm SAVED_INV_VARIANCE should not be set in inference mode")
+    else:
+        _require(sm is not None, ErrorCode.AttributeNotSet, "BatchNorm training requires SAVED_MEAN output")
+        _require(si is not None, ErrorCode.AttributeNotSet, "BatchNorm training requires SAVED_INV_VARIANCE output")
+    _require(a.epsilon is not None, ErrorCode.AttributeNotSet, "BatchNorm epsilon not set")
+    _require(a.epsilon.isScalar(), ErrorCode.InvalidAttribute, "BatchNorm epsilon must be a scalar constant")
+    _require(a.momentum is not None, ErrorCode.AttributeNotSet, "BatchNorm momentum not set")
+    _require(a.momentum.isScalar(), ErrorCode.InvalidAttribute, "BatchNorm momentum must be a scalar constant")
+    g._fill(n)
+    per_channel = [(scale, "SCALE"), (bias, "BIAS"), (mean, "MEAN"), (var, "VAR")]
+    if training:
+        per_channel += [(sm, "SAVED_MEAN"), (si, "SAVED_INV_VARIANCE")]
+    for t, _ in per_channel:
+        if t is None:
+            continue
+        if not t.dim:
+            t.setDim([x.dim[1]])
+        if not t.stride:
+            t.setStride([1])
+    if not y.dim:
+        y.setDim(x.dim)
+    if not y.stride:
+        y.setStride(x.stride)
+    _require(y.dim == x.dim, ErrorCode.InvalidAttribute,
+             "BatchNorm output Y tensor must have the same shape as input X tensor")
+    _require(_layout_ok(y), ErrorCode.NotImplemented, _not_cl(y))
+    for t, tn in per_channel:
+        if t is None:
+            continue
+        _require(t.dim == [x.dim[1]], ErrorCode.InvalidAttribute,
+                 f"BatchNorm tensor {tn} must be 1D with size equal to channel dimension C")
+        _require(t.stride == [1], ErrorCode.InvalidAttribute, f"BatchNorm tensor {tn} must have unit stride")
+
+
 _VALIDATORS = {
     Op.CONV_FPROP: _v_conv_fprop,
     Op.CONV_DGRAD: _v_conv_dgrad,
@@ -886,4 +961,5 @@ _VALIDATORS = {
     Op.RMSNORM: lambda g, n: _v_norm(g, n, "RmsNorm"),
     Op.REDUCTION: _v_reduction,
     Op.POINTWISE: _v_pointwise,
+    Op.BATCHNORM: _v_batchnorm,
 }

@@ -35,7 +35,7 @@ class fb_tensor_desc(ctypes.Structure):
 class fb_node_desc(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("op", ctypes.c_int32), ("mode", ctypes.c_int32),
                 ("flags", ctypes.c_int32), ("num_spatial", ctypes.c_int32),
-                ("inputs", ctypes.c_int32 * 4), ("outputs", ctypes.c_int32 * 3),
+                ("inputs", ctypes.c_int32 * 6), ("outputs", ctypes.c_int32 * 3),
                 ("reserved", ctypes.c_int32), ("padding", ctypes.c_int64 * 3),
                 ("stride", ctypes.c_int64 * 3), ("dilation", ctypes.c_int64 * 3),
                 ("fparams", ctypes.c_float * 4)]
@@ -272,9 +272,13 @@ class Graph(GraphBase):
             keep.append(nm)
             d.name = nm
             d.op = int(n.op)
-            ins = list(n.inputs) + [None] * (4 - len(n.inputs))
+            node_ins = list(n.inputs)
+            if n.op == Op.BATCHNORM:
+                node_ins = node_ins[:6]  # momentum is not a kernel operand: it goes into fparams
+                d.fparams[0] = float(n.inputs[6].getScalarValue())
+            ins = node_ins + [None] * (6 - len(node_ins))
             outs = list(n.outputs) + [None] * (3 - len(n.outputs))
-            for k in range(4):
+            for k in range(6):
                 d.inputs[k] = tid(ins[k])
             for k in range(3):
                 d.outputs[k] = tid(outs[k])
@@ -295,7 +299,7 @@ class Graph(GraphBase):
                     d.flags |= G.FLAG_SDPA_HAS_SCALE
                     d.fparams[0] = float(a.scale)
                 d.fparams[1] = float(a.dropout)
-            elif n.op in (Op.LAYERNORM, Op.RMSNORM):
+            elif n.op in (Op.LAYERNORM, Op.RMSNORM, Op.BATCHNORM):
                 if a.forwardPhase == NormFwdPhase.TRAINING:
                     d.flags |= G.FLAG_NORM_TRAINING
         outs_sorted = sorted((t for t in self.outputs if not t.isVirtual()), key=lambda t: t.name)

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 from typing import Tuple
 
-from .graph import (ConvDGradAttr, ConvFPropAttr, ConvWGradAttr, DataType, LayernormAttr, MatmulAttr,
+from .graph import (BatchnormAttr, ConvDGradAttr, ConvFPropAttr, ConvWGradAttr, DataType, LayernormAttr, MatmulAttr,
                     NormFwdPhase, PointwiseAttr, ReductionAttr, RmsnormAttr, SdpaAttr, TensorAttr,
                     channelsLastStride, contiguousStride)
 from .runtime import Graph
@@ -155,3 +155,35 @@ def row_sum(rows, cols, dtype=DataType.BFloat16, name="rowsum"):
     y.setName("y").setDim([rows, 1]).setStride([1, 1]).setOutput(True)
     g.validate()
     return g, {"x": x}, y
+
+
+def batchnorm_fwd(n, c, spatial, dtype=DataType.BFloat16, param_dtype=DataType.Float, train=False,
+                  channels_last=False, affine=True, running=True, name="batchnorm"):
+    """x [n, c, *spatial] (contiguous or channels-last), per-channel [c] parameters, as the reference's
+    samples/batchnorm/*.cpp build it."""
+    g = _new(name, dtype, dtype)
+    xd = [n, c] + list(spatial)
+    xs = channelsLastStride(xd) if channels_last else contiguousStride(xd)
+    x = g.tensor(TensorAttr().setName("x").setDim(xd).setStride(xs))
+    ins = {"x": x}
+
+    def per_channel(nm):
+        t = g.tensor(TensorAttr().setName(nm).setDim([c]).setStride([1]).setDataType(param_dtype))
+        ins[nm] = t
+        return t
+    sc = per_channel("gamma") if affine else None
+    bi = per_channel("beta") if affine else None
+    mean = per_channel("mean") if running else None
+    var = per_channel("var") if running else None
+    attr = BatchnormAttr().setForwardPhase(NormFwdPhase.TRAINING if train else NormFwdPhase.INFERENCE)
+    attr.setEpsilon(g.tensor(TensorAttr(1e-5).setName("eps"))).setMomentum(g.tensor(TensorAttr(0.1).setName("momentum")))
+    attr.setName("bn")
+    y, sm, si = g.batchnorm(x, sc, bi, mean, var, attr)
+    y.setName("y").setOutput(True)
+    outs = [y]
+    if train:
+        sm.setName("saved_mean").setOutput(True).setDataType(DataType.Float)
+        si.setName("saved_inv_var").setOutput(True).setDataType(DataType.Float)
+        outs += [sm, si]
+    g.validate()
+    return g, ins, outs

@@ -175,6 +175,29 @@ private:
   NormFwdPhase phase_ = NormFwdPhase::NOT_SET;
 };
 
+// reference attributes/batchnorm_attributes.h:27-90
+class BatchnormAttr : public AttributesCRTP<BatchnormAttr> {
+public:
+  enum class InputNames : uint8_t { X, SCALE, BIAS, MEAN, VAR, EPSILON, MOMENTUM };
+  enum class OutputNames : uint8_t { Y, SAVED_MEAN, SAVED_INV_VARIANCE };
+  FUSILLI_TENSOR_MAPS
+  FUSILLI_IN(BatchnormAttr, X, X)
+  FUSILLI_IN(BatchnormAttr, SCALE, SCALE)
+  FUSILLI_IN(BatchnormAttr, BIAS, BIAS)
+  FUSILLI_IN(BatchnormAttr, MEAN, MEAN)
+  FUSILLI_IN(BatchnormAttr, VAR, VAR)
+  FUSILLI_IN(BatchnormAttr, EPSILON, Epsilon)
+  FUSILLI_IN(BatchnormAttr, MOMENTUM, Momentum)
+  FUSILLI_OUT(BatchnormAttr, Y, Y)
+  FUSILLI_OUT(BatchnormAttr, SAVED_MEAN, SAVED_MEAN)
+  FUSILLI_OUT(BatchnormAttr, SAVED_INV_VARIANCE, SAVED_INV_VARIANCE)
+  BatchnormAttr &setForwardPhase(NormFwdPhase p) { phase_ = p; return *this; }
+  NormFwdPhase getForwardPhase() const { return phase_; }
+
+private:
+  NormFwdPhase phase_ = NormFwdPhase::NOT_SET;
+};
+
 class RmsnormAttr : public AttributesCRTP<RmsnormAttr> {
 public:
   enum class InputNames : uint8_t { X, SCALE, EPSILON };

@@ -218,6 +218,20 @@ public:
     nodes_.push_back(std::make_unique<LayerNormNode>(std::move(a), context));
     return {y, m, v};
   }
+  std::array<TensorPtr, 3> batchnorm(const TensorPtr &x, const TensorPtr &scale, const TensorPtr &bias,
+                                     const TensorPtr &mean, const TensorPtr &var, BatchnormAttr &a) {
+    autoName(a, "batchnorm", {{"X", x}, {"SCALE", scale}, {"BIAS", bias}, {"MEAN", mean}, {"VAR", var},
+                              {"EPSILON", a.getEpsilon()}, {"MOMENTUM", a.getMomentum()}});
+    auto y = outputTensor(a.getName() + "_Y");
+    TensorPtr sm, si;
+    if (a.getForwardPhase() == NormFwdPhase::TRAINING) {
+      sm = outputTensor(a.getName() + "_SAVED_MEAN");
+      si = outputTensor(a.getName() + "_SAVED_INV_VARIANCE");
+    }
+    a.setX(x).setSCALE(scale).setBIAS(bias).setMEAN(mean).setVAR(var).setY(y).setSAVED_MEAN(sm).setSAVED_INV_VARIANCE(si);
+    nodes_.push_back(std::make_unique<BatchNormNode>(std::move(a), context));
+    return {y, sm, si};
+  }
   std::array<TensorPtr, 2> rmsnorm(const TensorPtr &x, const TensorPtr &scale, RmsnormAttr &a) {
     autoName(a, "rmsnorm", {{"X", x}, {"SCALE", scale}, {"EPSILON", a.getEpsilon()}});
     auto y = outputTensor(a.getName() + "_Y");

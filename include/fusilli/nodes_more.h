@@ -516,6 +516,111 @@ public:
   }
 };
 
+// ---- batch normalisation (reference node/batchnorm_node.h:33-247) ------------------------------
+class BatchNormNode : public INode {
+public:
+  BatchnormAttr batchnormAttr;
+  BatchNormNode(BatchnormAttr &&a, const Context &ctx) : INode(ctx), batchnormAttr(std::move(a)) {}
+  const std::string &getName() const override { return batchnormAttr.getName(); }
+  Type getType() const override { return Type::BatchNorm; }
+  bool isTrainingForwardPhase() const { return batchnormAttr.getForwardPhase() == NormFwdPhase::TRAINING; }
+
+  ErrorObject preValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Pre-Validating BatchNormNode '" << getName() << "'");
+    const auto &a = batchnormAttr;
+    FUSILLI_RETURN_ERROR_IF(a.getForwardPhase() == NormFwdPhase::NOT_SET, ErrorCode::AttributeNotSet,
+                            "BatchNorm forward phase not set");
+    TensorPtr x = a.getX(), y = a.getY();
+    FUSILLI_RETURN_ERROR_IF(!x, ErrorCode::AttributeNotSet, "BatchNorm input tensor X not set");
+    FUSILLI_RETURN_ERROR_IF(!y, ErrorCode::AttributeNotSet, "BatchNorm output tensor Y not set");
+    FUSILLI_RETURN_ERROR_IF(x->getDim().size() < 2, ErrorCode::InvalidAttribute,
+                            "BatchNorm input tensor X must have a rank of at least 2");
+    FUSILLI_CHECK_ERROR(detail::requireLayout(x));
+    if (!isTrainingForwardPhase()) {
+      FUSILLI_RETURN_ERROR_IF(!a.getMEAN(), ErrorCode::AttributeNotSet, "BatchNorm inference requires running MEAN");
+      FUSILLI_RETURN_ERROR_IF(!a.getVAR(), ErrorCode::AttributeNotSet, "BatchNorm inference requires running VAR");
+      FUSILLI_RETURN_ERROR_IF(a.getSAVED_MEAN() != nullptr, ErrorCode::InvalidAttribute,
+                              "BatchNorm SAVED_MEAN should not be set in inference mode");
+      FUSILLI_RETURN_ERROR_IF(a.getSAVED_INV_VARIANCE() != nullptr, ErrorCode::InvalidAttribute,
+                              "BatchNorm SAVED_INV_VARIANCE should not be set in inference mode");
+    } else {
+      FUSILLI_RETURN_ERROR_IF(!a.getSAVED_MEAN(), ErrorCode::AttributeNotSet,
+                              "BatchNorm training requires SAVED_MEAN output");
+      FUSILLI_RETURN_ERROR_IF(!a.getSAVED_INV_VARIANCE(), ErrorCode::AttributeNotSet,
+                              "BatchNorm training requires SAVED_INV_VARIANCE output");
+    }
+    TensorPtr e = a.getEpsilon(), m = a.getMomentum();
+    FUSILLI_RETURN_ERROR_IF(!e, ErrorCode::AttributeNotSet, "BatchNorm epsilon not set");
+    FUSILLI_RETURN_ERROR_IF(!e->isScalar(), ErrorCode::InvalidAttribute, "BatchNorm epsilon must be a scalar constant");
+    FUSILLI_RETURN_ERROR_IF(!m, ErrorCode::AttributeNotSet, "BatchNorm momentum not set");
+    FUSILLI_RETURN_ERROR_IF(!m->isScalar(), ErrorCode::InvalidAttribute, "BatchNorm momentum must be a scalar constant");
+    return ok();
+  }
+  ErrorObject inferPropertiesNode() override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Inferring properties for BatchNormNode '" << getName() << "'");
+    auto &a = batchnormAttr;
+    a.fillFromContext(context);
+    TensorPtr x = a.getX(), y = a.getY();
+    const std::vector<int64_t> perChannel = {x->getDim()[1]}, unit = {1};
+    for (const TensorPtr &t : perChannelTensors()) {
+      if (!t) continue;
+      if (t->getDim().empty()) t->setDim(perChannel);
+      if (t->getStride().empty()) t->setStride(unit);
+    }
+    if (y->getDim().empty()) y->setDim(x->getDim());
+    if (y->getStride().empty()) y->setStride(x->getStride());
+    return ok();
+  }
+  ErrorObject postValidateNode() const override {
+    FUSILLI_LOG_LABEL_ENDL("INFO: Post-Validating BatchNormNode '" << getName() << "'");
+    const auto &a = batchnormAttr;
+    TensorPtr x = a.getX(), y = a.getY();
+    FUSILLI_RETURN_ERROR_IF(x->getDim() != y->getDim(), ErrorCode::InvalidAttribute,
+                            "BatchNorm output Y tensor must have the same shape as input X tensor");
+    FUSILLI_CHECK_ERROR(detail::requireLayout(y));
+    static const char *const names[] = {"SCALE", "BIAS", "MEAN", "VAR", "SAVED_MEAN", "SAVED_INV_VARIANCE"};
+    const std::vector<int64_t> perChannel = {x->getDim()[1]}, unit = {1};
+    const auto tensors = perChannelTensors();
+    for (size_t i = 0; i < tensors.size(); ++i) {
+      if (!tensors[i]) continue;
+      FUSILLI_RETURN_ERROR_IF(tensors[i]->getDim() != perChannel, ErrorCode::InvalidAttribute,
+                              std::string("BatchNorm tensor ") + names[i] +
+                                  " must be 1D with size equal to channel dimension C");
+      FUSILLI_RETURN_ERROR_IF(tensors[i]->getStride() != unit, ErrorCode::InvalidAttribute,
+                              std::string("BatchNorm tensor ") + names[i] + " must have unit stride");
+    }
+    return ok();
+  }
+  void describe(fb_node_desc &d, const TensorId &id) const override {
+    detail::initDesc(d, FB_OP_BATCHNORM);
+    const auto &a = batchnormAttr;
+    d.inputs[0] = id(a.getX());
+    d.inputs[1] = id(a.getSCALE());
+    d.inputs[2] = id(a.getBIAS());
+    d.inputs[3] = id(a.getMEAN());
+    d.inputs[4] = id(a.getVAR());
+    d.inputs[5] = id(a.getEpsilon());
+    d.outputs[0] = id(a.getY());
+    d.outputs[1] = id(a.getSAVED_MEAN());
+    d.outputs[2] = id(a.getSAVED_INV_VARIANCE());
+    if (isTrainingForwardPhase()) d.flags |= FB_FLAG_NORM_TRAINING;
+    // functional op: momentum reaches no output; kept in the plan for the record
+    if (a.getMomentum()) d.fparams[0] = static_cast<float>(a.getMomentum()->scalarAsDouble());
+  }
+
+private:
+  // SCALE, BIAS, MEAN, VAR and, in training, the two saved statistics: all [C] with unit stride
+  std::vector<TensorPtr> perChannelTensors() const {
+    const auto &a = batchnormAttr;
+    std::vector<TensorPtr> t = {a.getSCALE(), a.getBIAS(), a.getMEAN(), a.getVAR()};
+    if (isTrainingForwardPhase()) {
+      t.push_back(a.getSAVED_MEAN());
+      t.push_back(a.getSAVED_INV_VARIANCE());
+    }
+    return t;
+  }
+};
+
 // ---- custom op (reference attributes/custom_op_attributes.h:23-110, node/custom_op_node.h) ------
 // A node whose body is a piece of torch-dialect MLIR supplied by the user. The builders and
 // validate() accept it as the reference does (its checks need no compiler); this backend has no

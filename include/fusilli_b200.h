@@ -35,7 +35,7 @@ extern "C" {
 
 #define FB_ABI_VERSION 2
 #define FB_MAX_RANK 8
-#define FB_MAX_NODE_INPUTS 4
+#define FB_MAX_NODE_INPUTS 6
 #define FB_MAX_NODE_OUTPUTS 3
 
 /* Status codes: same numbering as fusilli::ErrorCode (logging.h:58-71). */
@@ -83,7 +83,8 @@ enum {
   FB_OP_LAYERNORM = 6,
   FB_OP_RMSNORM = 7,
   FB_OP_REDUCTION = 8,
-  FB_OP_POINTWISE = 9
+  FB_OP_POINTWISE = 9,
+  FB_OP_BATCHNORM = 10
 };
 
 /* Pointwise modes: same order as PointwiseAttr::Mode
@@ -201,11 +202,16 @@ typedef struct fb_tensor_desc {
  *   SDPA        in {Q, K, V, MASK}     out {O}
  *   LAYERNORM   in {X, SCALE, BIAS, EPSILON}  out {Y, MEAN, INV_VARIANCE}
  *   RMSNORM     in {X, SCALE, EPSILON}        out {Y}
+ *   BATCHNORM   in {X, SCALE, BIAS, MEAN, VAR, EPSILON}  out {Y, SAVED_MEAN, SAVED_INV_VARIANCE}
+ *               (FB_FLAG_NORM_TRAINING: batch statistics; else the running MEAN / VAR)
  *   REDUCTION   in {X}                 out {Y}
  *   POINTWISE   in {IN_0, IN_1, IN_2}  out {OUT_0}
  * fparams by op:
  *   POINTWISE   {elu_alpha, softplus_beta, softplus_threshold, swish_beta}
- *   SDPA        {scale (valid with FB_FLAG_SDPA_HAS_SCALE), dropout_p} */
+ *   SDPA        {scale (valid with FB_FLAG_SDPA_HAS_SCALE), dropout_p}
+ *   BATCHNORM   {momentum} (carried for the record: the op is functional, as
+ *               torch.aten.native_batch_norm on value tensors, and returns no
+ *               updated running statistics) */
 typedef struct fb_node_desc {
   const char *name;
   int32_t op;

@@ -251,6 +251,31 @@ def pointwise(mode: int, ins, out_shape, integral: bool, prm) -> np.ndarray:
     return out
 
 
+def batchnorm(x, scale, bias, mean, var, eps: float, training: bool):
+    """torch.aten.native_batch_norm on value tensors, the op the reference emits
+    (include/fusilli/support/asm_emitter.h:1283-1284): per-channel statistics over every dim but 1.
+    Training uses the batch's mean and biased variance and returns them as (mean, 1/sqrt(var+eps));
+    inference uses the given running mean / var. No running statistics are returned, so momentum
+    has no effect. float64 accumulation."""
+    xd = np.asarray(x, dtype=np.float64)
+    c = xd.shape[1]
+    axes = tuple(i for i in range(xd.ndim) if i != 1)
+    shape = [1, c] + [1] * (xd.ndim - 2)
+    if training:
+        m = xd.mean(axis=axes)
+        v = xd.var(axis=axes)  # biased
+    else:
+        m = np.asarray(mean, dtype=np.float64).reshape(c)
+        v = np.asarray(var, dtype=np.float64).reshape(c)
+    inv = 1.0 / np.sqrt(v + eps)
+    y = (xd - m.reshape(shape)) * inv.reshape(shape)
+    if scale is not None:
+        y = y * np.asarray(scale, dtype=np.float64).reshape(shape)
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64).reshape(shape)
+    return y.astype(np.float32), m.astype(np.float32), inv.astype(np.float32)
+
+
 # ---- graph interpreter -----------------------------------------------------------
 def execute(graph: GraphBase, inputs: Dict[TensorAttr, np.ndarray]) -> Dict[TensorAttr, np.ndarray]:
     """Runs a validated graph. ``inputs`` maps each non-scalar graph input to its
@@ -305,6 +330,14 @@ def execute(graph: GraphBase, inputs: Dict[TensorAttr, np.ndarray]) -> Dict[Tens
             if tr:
                 put(n.outputs[1], mean)
                 put(n.outputs[2], rstd)
+        elif n.op == Op.BATCHNORM:
+            x, sc, bi, mean, var, e, _momentum = n.inputs
+            tr = a.forwardPhase == NormFwdPhase.TRAINING
+            y, sm, si = batchnorm(get(x), get(sc), get(bi), get(mean), get(var), float(e.getScalarValue()), tr)
+            put(n.outputs[0], y)
+            if tr:
+                put(n.outputs[1], sm)
+                put(n.outputs[2], si)
         elif n.op == Op.RMSNORM:
             x, s, e = n.inputs
             put(n.outputs[0], rmsnorm(get(x), get(s), float(e.getScalarValue())))

@@ -30,7 +30,7 @@ OWN_SOURCES = ["test_frontend_host.cpp", "test_frontend_device.cpp"]
 
 # Reference programs that only need the graph API of the operators in scope. Paths are relative
 # to the reference checkout. SDPA samples there go through a user-supplied MLIR custom op and
-# batchnorm / custom ops are outside this backend, so they are not listed. Of the dynamic-shape
+# custom ops need an MLIR compiler, so they are not listed. Of the dynamic-shape
 # samples, the reduction one is an expected failure in the reference itself (it requires the
 # IREE-specific non-zero transient size) and the custom-op one needs MLIR.
 REFERENCE_SAMPLES = [
@@ -70,6 +70,11 @@ REFERENCE_SAMPLES = [
     "samples/rmsnorm/rmsnorm_infer_nchw.cpp",
     "samples/rmsnorm/rmsnorm_infer_nchw_scale.cpp",
     "samples/rmsnorm/rmsnorm_infer_nhwc_scale.cpp",
+    "samples/batchnorm/batchnorm_infer_nchw.cpp",
+    "samples/batchnorm/batchnorm_infer_nchw_scale_bias.cpp",
+    "samples/batchnorm/batchnorm_infer_nhwc_scale_bias.cpp",
+    "samples/batchnorm/batchnorm_train_nchw.cpp",
+    "samples/batchnorm/batchnorm_train_nchw_scale_bias.cpp",
     "samples/dynamic_shapes/conv_fprop_dynamic_batch.cpp",
     "samples/dynamic_shapes/sdpa_basic_dynamic_sequence.cpp",
 ]
@@ -111,12 +116,14 @@ REFERENCE_HOST_TESTS = [
     "tests/test_pointwise_attributes.cpp",
     "tests/test_pointwise_node.cpp",
     "tests/test_int_types.cpp",
+    "tests/test_batchnorm_attributes.cpp",
+    "tests/test_batchnorm_node.cpp",
 ]
 # Not listed, because they exercise parts this backend does not have: test_graph (MLIR emission and
 # the IREE compile cache), test_handle / test_buffer / test_utils (CPU and AMDGPU HAL devices),
 # test_compile_*, test_dllib, test_process, test_memstream, test_extras, test_logging (compiler
 # driver plumbing), test_float_types (software float types; half and bf16 are the compiler's native
-# types here), batchnorm and custom ops.
+# types here) and custom ops.
 
 
 def _flags():

@@ -9,6 +9,7 @@ native_layer_norm :1427-1503, aten.rms_norm :1592-1626, reductions
 The reference itself (IREE llvm-cpu) cannot run on this machine, so these are
 the closest executable statement of the semantics it lowers to. Run once:
     python tests/golden/make_golden.py
+    python tests/golden/make_golden.py --batchnorm     (batchnorm_golden.npz, aten.native_batch_norm :1232-1307)
 Inputs are float32 and computed in float64 so the vectors carry no
 accumulation-order noise; tests compare the oracle to them at 1e-5.
 """
@@ -133,5 +134,39 @@ def main():
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")
 
 
+OUT_BN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "batchnorm_golden.npz")
+
+
+def main_batchnorm():
+    """tests/golden/batchnorm_golden.npz: aten.native_batch_norm, the op BatchNormNode lowers to
+    (asm_emitter.h:1283-1284), in both phases, 4-D and 5-D, with and without the optional operands.
+    A file and a seed of its own, so the vectors above stay byte-identical."""
+    torch.manual_seed(4321)
+    g = {}
+    d = torch.float64
+    for nm, shape in (("4d", (3, 5, 4, 6)), ("5d", (2, 3, 2, 3, 4)), ("2d", (7, 4))):
+        c = shape[1]
+        x = torch.rand(*shape, dtype=torch.float32) * 4 - 1
+        w = torch.rand(c) + 0.5
+        b = torch.rand(c) - 0.5
+        rm = torch.rand(c) - 0.5
+        rv = torch.rand(c) + 0.25
+        g[f"bn_{nm}_x"], g[f"bn_{nm}_w"], g[f"bn_{nm}_b"] = x.numpy(), w.numpy(), b.numpy()
+        g[f"bn_{nm}_rm"], g[f"bn_{nm}_rv"] = rm.numpy(), rv.numpy()
+        y, _, _ = torch.ops.aten.native_batch_norm(x.to(d), w.to(d), b.to(d), rm.to(d), rv.to(d), False, 0.1, 1e-5)
+        g[f"bn_{nm}_infer_y"] = y.float().numpy()
+        y, sm, si = torch.ops.aten.native_batch_norm(x.to(d), w.to(d), b.to(d), None, None, True, 0.1, 1e-5)
+        g[f"bn_{nm}_train_y"], g[f"bn_{nm}_train_mean"], g[f"bn_{nm}_train_invstd"] = (
+            y.float().numpy(), sm.float().numpy(), si.float().numpy())
+        y, sm, si = torch.ops.aten.native_batch_norm(x.to(d), None, None, None, None, True, 0.1, 1e-5)
+        g[f"bn_{nm}_plain_y"] = y.float().numpy()
+    np.savez_compressed(OUT_BN, **g)
+    print("wrote", OUT_BN, os.path.getsize(OUT_BN), "bytes,", len(g), "arrays")
+
+
 if __name__ == "__main__":
-    main()
+    import sys
+    if "--batchnorm" in sys.argv:
+        main_batchnorm()
+    else:
+        main()

@@ -150,6 +150,53 @@ def matmul_int4_fp16():
     return g, {a: ones, bt: _fill(bt, 1.0)}, lambda o: np.all(o[c] == np.float16(k))
 
 
+def batchnorm_infer_nchw_scale_bias():
+    """samples/batchnorm/batchnorm_infer_nchw_scale_bias.cpp with batchnorm_utils.h:25-50: x = c + 1,
+    running mean 0 and var 1 -> y = scale * x / sqrt(1 + eps) + bias."""
+    n, c, h, w, eps, scale, bias = 2, 3, 4, 4, 1e-5, 2.0, 1.0
+    g = fz.Graph()
+    g.setName("kat_bn_infer").setIODataType(F32).setComputeDataType(F32)
+    x = g.tensor(TensorAttr().setName("x").setDim([n, c, h, w]).setStride(contiguousStride([n, c, h, w])))
+    ts = {k: g.tensor(TensorAttr().setName(k).setDim([c]).setStride([1])) for k in ("scale", "bias", "mean", "var")}
+    attr = fz.BatchnormAttr().setForwardPhase(fz.NormFwdPhase.INFERENCE).setName("batchnorm")
+    attr.setEpsilon(g.tensor(TensorAttr(eps).setName("epsilon"))).setMomentum(g.tensor(TensorAttr(0.1).setName("momentum")))
+    y, _, _ = g.batchnorm(x, ts["scale"], ts["bias"], ts["mean"], ts["var"], attr)
+    y.setName("y").setOutput(True)
+    g.validate()
+    xv = np.repeat(np.tile(np.arange(1, c + 1, dtype=np.float32), n), h * w)
+    want = scale * xv / np.float32(math.sqrt(1.0 + eps)) + bias
+    ins = {x: xv, ts["scale"]: _fill(ts["scale"], scale), ts["bias"]: _fill(ts["bias"], bias),
+           ts["mean"]: _fill(ts["mean"], 0.0), ts["var"]: _fill(ts["var"], 1.0)}
+    return g, ins, lambda o: np.max(np.abs(o[y] - want)) < 1e-4
+
+
+def batchnorm_train_nchw_two_value():
+    """samples/batchnorm/batchnorm_train_nchw.cpp with batchnorm_utils.h:58-91: half of every channel
+    is -1 and half +1 -> mean 0, var 1, y = x / sqrt(1 + eps), saved statistics (0, 1/sqrt(1+eps))."""
+    n, c, h, w, eps = 2, 3, 4, 4, 1e-5
+    g = fz.Graph()
+    g.setName("kat_bn_train").setIODataType(F32).setComputeDataType(F32)
+    x = g.tensor(TensorAttr().setName("x").setDim([n, c, h, w]).setStride(contiguousStride([n, c, h, w])))
+    attr = fz.BatchnormAttr().setForwardPhase(fz.NormFwdPhase.TRAINING).setName("batchnorm")
+    attr.setEpsilon(g.tensor(TensorAttr(eps).setName("epsilon"))).setMomentum(g.tensor(TensorAttr(0.1).setName("momentum")))
+    y, sm, si = g.batchnorm(x, None, None, None, None, attr)
+    y.setName("y").setOutput(True)
+    sm.setName("saved_mean").setOutput(True)
+    si.setName("saved_inv_var").setOutput(True)
+    g.validate()
+    xv = np.empty((n, c, h, w), np.float32)
+    for ni in range(n):
+        for hi in range(h):
+            for wi in range(w):
+                xv[ni, :, hi, wi] = -1.0 if ni * h * w + hi * w + wi < n * h * w // 2 else 1.0
+    inv = np.float32(1.0 / math.sqrt(1.0 + eps))
+
+    def check(o):
+        return (np.max(np.abs(o[y] - xv.reshape(-1) * inv)) < 1e-4 and np.max(np.abs(o[sm])) < 1e-4
+                and np.max(np.abs(o[si] - inv)) < 1e-4)
+    return g, {x: xv.reshape(-1)}, check
+
+
 def _sdpa_case(name, causal=False, mask=False, hk=8, hv=8, sq=64, skv=64):
     """samples/sdpa/*.cpp against samples/sdpa_utils.cpp:49-102 (constant fills 0.01):
     softmax over equal scores is uniform, so every output element equals the V fill."""
@@ -284,6 +331,8 @@ CASES = {
     "matmul_batched_bias": matmul_batched_bias,
     "matmul_transposed_b_f16": matmul_transposed_b_f16,
     "matmul_int4_fp16": matmul_int4_fp16,
+    "batchnorm_infer_nchw_scale_bias": batchnorm_infer_nchw_scale_bias,
+    "batchnorm_train_nchw_two_value": batchnorm_train_nchw_two_value,
     "sdpa_mha": lambda: _sdpa_case("kat_sdpa_mha"),
     "sdpa_causal": lambda: _sdpa_case("kat_sdpa_causal", causal=True),
     "sdpa_mask": lambda: _sdpa_case("kat_sdpa_mask", mask=True),

@@ -83,6 +83,9 @@ CASES = [
     ("rmsnorm_rows", lambda r: wl.rmsnorm_infer(r, 1024), 0, ("gamma",), 64, [8, 33, 64]),
     ("rowsum_rows", lambda r: wl.row_sum(r, 384), 0, (), 64, [8, 33, 64]),
     ("reduction_min_batch_i32", lambda n: reduction_min(n), 0, (), 2, [1, 2, 5]),
+    ("batchnorm_train_batch_nhwc", lambda n: wl.batchnorm_fwd(n, 32, [6, 5], DataType.Float, train=True,
+                                                               channels_last=True, running=False),
+     0, ("gamma", "beta", "saved_mean", "saved_inv_var"), 8, [2, 5, 8]),
     ("pointwise_chain_batch", lambda n: add_bias_rows(n), 0, ("bias",), 6, [1, 4, 6]),
 ]
 

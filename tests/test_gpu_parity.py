@@ -202,6 +202,28 @@ def test_matmul_int4_operand(cfg):
     assert "gemm_tcgen05" not in g.statistics()
 
 
+# ---- batch normalisation -------------------------------------------------------------
+@pytest.mark.parametrize("cfg", [
+    dict(n=4, c=8, spatial=[5, 6], dtype=F32, train=False),
+    dict(n=4, c=8, spatial=[5, 6], dtype=F32, train=True),
+    dict(n=4, c=8, spatial=[5, 6], dtype=F32, train=True, channels_last=True),
+    dict(n=16, c=64, spatial=[28, 28], dtype=BF16, train=True, channels_last=True),   # several slices per channel block
+    dict(n=16, c=64, spatial=[28, 28], dtype=BF16, train=True),
+    dict(n=8, c=48, spatial=[14, 14], dtype=F16, train=False, channels_last=True),
+    dict(n=2, c=3, spatial=[4, 5, 6], dtype=F32, train=True),                         # 5-D
+    dict(n=2, c=3, spatial=[4, 5, 6], dtype=F32, train=True, channels_last=True),
+    dict(n=64, c=40, spatial=[], dtype=F32, train=True),                              # [N, C]
+    dict(n=8, c=16, spatial=[7, 7], dtype=F32, train=True, affine=False, running=False),
+    dict(n=8, c=16, spatial=[7, 7], dtype=BF16, train=False, affine=False),
+    dict(n=32, c=256, spatial=[56, 56], dtype=BF16, train=True, channels_last=True),  # 51 M elements
+])
+def test_batchnorm(cfg):
+    g, ins, outs = wl.batchnorm_fwd(**cfg)
+    data = _inputs(ins, 31, ("uniform", -1.0, 3.0), per={"var": ("uniform", 0.25, 2.0)})
+    check_graph(g, data, scale_atol=4.0 if cfg["dtype"] != F32 else 20.0)
+    assert g.numLaunches() == (3 if cfg["train"] else 1)
+
+
 # ---- sdpa ---------------------------------------------------------------------------
 @pytest.mark.parametrize("cfg", [
     dict(b=1, h=8, s=64, d=64, dtype=F16, causal=False),

@@ -17,7 +17,7 @@ import numpy as np
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["matmul", "conv_fprop", "conv_dgrad", "conv_wgrad", "sdpa", "layernorm",
-                                   "rmsnorm", "rowsum"])
+                                   "rmsnorm", "rowsum", "batchnorm_train", "batchnorm_infer"])
     for name, default in (("b", 1), ("m", 4096), ("n", 4096), ("k", 4096), ("c", 64), ("hw", 56), ("kout", 64),
                           ("r", 3), ("h", 8), ("s", 4096), ("rows", 8192), ("cols", 8192), ("iters", 3),
                           ("warmup", 1)):
@@ -70,6 +70,17 @@ def main():
         outs = [(out, torch.empty(a.b, a.h, a.s, 128, device="cuda", dtype=bf))]
         pairs = a.s * (a.s + 1) / 2 if not a.non_causal else a.s * a.s
         work, unit = 4.0 * a.b * a.h * 128 * pairs, "TFLOP/s"
+    elif a.op.startswith("batchnorm"):
+        # channels-last bf16 [n, c, hw, hw]; algorithmic bytes: training reads x twice and writes y
+        train = a.op == "batchnorm_train"
+        g, ins, o = wl.batchnorm_fwd(a.n, a.c, [a.hw, a.hw], train=train, channels_last=True)
+        x = rnd(a.n, a.hw, a.hw, a.c)
+        tens = {"x": x, "gamma": torch.ones(a.c, device="cuda"), "beta": torch.zeros(a.c, device="cuda"),
+                "mean": torch.zeros(a.c, device="cuda"), "var": torch.ones(a.c, device="cuda")}
+        outs = [(o[0], torch.empty_like(x))]
+        if train:
+            outs += [(o[1], torch.empty(a.c, device="cuda")), (o[2], torch.empty(a.c, device="cuda"))]
+        work, unit = (3.0 if train else 2.0) * x.numel() * 2, "GB/s"
     else:
         x = rnd(a.rows, a.cols)
         gam = torch.ones(a.cols, device="cuda")

@@ -264,7 +264,7 @@ __global__ void __launch_bounds__(256) contract_simt_kernel(const ContractParams
 // 16-byte load per pixel row instead of a full coordinate decomposition per element. Tile 128
 // pixels x 64 output channels x 16, 8 x 4 outputs per thread, next tile prefetched in registers.
 constexpr int FBM = 128, FBN = 64, FBK = 16;
-__global__ void __launch_bounds__(256) conv_fprop_cl_f32_kernel(const ContractParams p) {
+__global__ void __launch_bounds__(256, 3) conv_fprop_cl_f32_kernel(const ContractParams p) {
   __shared__ __align__(16) float As[FBK][FBM + 4];
   __shared__ __align__(16) float Bs[FBK][FBN + 4];
   const ConvGeomDev &q = p.g;
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(256) conv_fprop_cl_f32_kernel(const ContractPa
   const float *x = static_cast<const float *>(p.a), *wt = static_cast<const float *>(p.b);
   // staging: two pixel rows and one filter row per thread, four consecutive channels each
   const int k4 = (tid & 3) * 4;
-  int64_t a_base[2];
+  const float *a_img[2]; // image base of the row's pixel (channel group applied)
   int a_ih0[2], a_iw0[2];
   bool a_ok[2];
 #pragma unroll
@@ -283,31 +283,47 @@ __global__ void __launch_bounds__(256) conv_fprop_cl_f32_kernel(const ContractPa
     a_ok[i] = m < p.M;
     int n, od, oh, ow;
     split_pos(a_ok[i] ? m : 0, q.OD, q.OH, q.OW, n, od, oh, ow);
-    a_base[i] = (int64_t)n * q.xs[0] + (int64_t)g * q.Cg;
+    a_img[i] = x + (int64_t)n * q.xs[0] + (int64_t)g * q.Cg + k4;
     a_ih0[i] = oh * q.sh - q.ph;
     a_iw0[i] = ow * q.sw - q.pw;
   }
   const int b_n = n0 + (tid >> 2);
   const bool b_ok = b_n < p.N;
-  const int64_t b_base = (int64_t)(g * q.Kg + (b_ok ? b_n : 0)) * q.ws[0];
+  const float *b_row = wt + (int64_t)(g * q.Kg + (b_ok ? b_n : 0)) * q.ws[0] + k4;
   const int tx = tid & 15, ty = tid >> 4; // outputs: rows ty*8 .. +7, columns tx*4 .. +3
   float acc[8][4] = {};
   float4 ra[2], rb;
-  auto fetch_tile = [&](int k0) {
-    const int tap = k0 / q.Cg, c0 = k0 - tap * q.Cg + k4;
-    const int r = tap / q.S, ss = tap - r * q.S;
+  // The reduction walks (filter row, filter column, 16-channel block) with counters: per tap one
+  // bounds test and one pointer per staged row, per block one 16-byte load per row.
+  int tr = 0, ts = 0, c0 = 0;
+  const float *a_tap[2], *b_tap;
+  auto enter_tap = [&]() {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const int ih = a_ih0[i] + r * q.dh, iw = a_iw0[i] + ss * q.dw;
+      const int ih = a_ih0[i] + tr * q.dh, iw = a_iw0[i] + ts * q.dw;
       const bool in = a_ok[i] && ih >= 0 && ih < q.H && iw >= 0 && iw < q.W;
-      ra[i] = in ? __ldg(reinterpret_cast<const float4 *>(x + a_base[i] + (int64_t)ih * q.xs[3] + (int64_t)iw * q.xs[4] + c0))
-                 : make_float4(0.f, 0.f, 0.f, 0.f);
+      a_tap[i] = in ? a_img[i] + (int64_t)ih * q.xs[3] + (int64_t)iw * q.xs[4] : nullptr;
     }
-    rb = b_ok ? __ldg(reinterpret_cast<const float4 *>(wt + b_base + (int64_t)r * q.ws[3] + (int64_t)ss * q.ws[4] + c0))
-              : make_float4(0.f, 0.f, 0.f, 0.f);
+    b_tap = b_ok ? b_row + (int64_t)tr * q.ws[3] + (int64_t)ts * q.ws[4] : nullptr;
+  };
+  auto fetch_tile = [&]() {
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      ra[i] = a_tap[i] ? __ldg(reinterpret_cast<const float4 *>(a_tap[i] + c0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    rb = b_tap ? __ldg(reinterpret_cast<const float4 *>(b_tap + c0)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    c0 += FBK;
+    if (c0 == q.Cg) {
+      c0 = 0;
+      if (++ts == q.S) {
+        ts = 0;
+        ++tr;
+      }
+      enter_tap();
+    }
   };
   const int K = (int)p.K;
-  fetch_tile(0);
+  enter_tap();
+  fetch_tile();
   for (int k0 = 0; k0 < K; k0 += FBK) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -316,7 +332,7 @@ __global__ void __launch_bounds__(256) conv_fprop_cl_f32_kernel(const ContractPa
     }
     Bs[k4 + 0][tid >> 2] = rb.x; Bs[k4 + 1][tid >> 2] = rb.y; Bs[k4 + 2][tid >> 2] = rb.z; Bs[k4 + 3][tid >> 2] = rb.w;
     __syncthreads();
-    if (k0 + FBK < K) fetch_tile(k0 + FBK);
+    if (k0 + FBK < K) fetch_tile();
 #pragma unroll
     for (int kk = 0; kk < FBK; ++kk) {
       const float4 a0 = *reinterpret_cast<const float4 *>(&As[kk][ty * 8]);
@@ -330,14 +346,55 @@ __global__ void __launch_bounds__(256) conv_fprop_cl_f32_kernel(const ContractPa
     }
     __syncthreads();
   }
+  // Epilogue: the pixel decomposition and every operand's offset are taken once per output row;
+  // the four channels of a row differ only in the channel term.
+  const EpilogueDev &e = p.epi;
+  const int ko0 = g * q.Kg + n0 + tx * 4;
+  const bool row_vec = e.out_dtype == FB_DT_FLOAT && q.ys[1] == 1 && n0 + tx * 4 + 3 < p.N &&
+                       (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && (ko0 & 3) == 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int m = m0 + ty * 8 + i;
-    if (m >= p.M) continue;
+    if (m >= p.M) break;
+    int n, od, oh, ow;
+    split_pos(m, q.OD, q.OH, q.OW, n, od, oh, ow);
+    const int sp[3] = {od, oh, ow};
+    const int64_t out_row = n * q.ys[0] + od * q.ys[2] + oh * q.ys[3] + ow * q.ys[4];
+    int64_t op_row[kMaxEpiOps], op_cs[kMaxEpiOps];
+#pragma unroll
+    for (int o = 0; o < kMaxEpiOps; ++o) {
+      op_row[o] = 0;
+      op_cs[o] = 0;
+      if (o < e.num_ops && e.ops[o].operand_kind == 1) {
+        int64_t off = n * e.ops[o].strides[0];
+        for (int d = 0; d < q.nsp; ++d) off += sp[3 - q.nsp + d] * e.ops[o].strides[2 + d];
+        op_row[o] = off;
+        op_cs[o] = e.ops[o].strides[1];
+      }
+    }
+    float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int nn = n0 + tx * 4 + j;
-      if (nn < p.N) store_out(p, g, m, nn, acc[i][j]);
+      const int ko = ko0 + j;
+      float r = round_to(acc[i][j], e.acc_round_dtype);
+#pragma unroll
+      for (int o = 0; o < kMaxEpiOps; ++o) {
+        if (o >= e.num_ops) break;
+        const EpiOpDev &op = e.ops[o];
+        float other = 0.f;
+        if (op.operand_kind == 1) other = load_f(op.operand, op.operand_dtype, op_row[o] + ko * op_cs[o]);
+        else if (op.operand_kind == 2) other = op.scalar;
+        const float a = op.value_is_in1 ? other : r, b = op.value_is_in1 ? r : other;
+        r = round_to(pw_apply_f(op.mode, a, b, 0.f, op.fparams), op.round_dtype);
+      }
+      v[j] = r;
+    }
+    if (row_vec) {
+      *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + out_row + ko0) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n0 + tx * 4 + j < p.N) store_f(p.out, e.out_dtype, out_row + (int64_t)(ko0 + j) * q.ys[1], v[j]);
     }
   }
 }

@@ -35,7 +35,13 @@ inline ErrorObject fromStatus(fb_status st) {
 class Handle {
 public:
   static ErrorOr<Handle> create(Backend backend) { return open(backend, 0, 0, false); }
-  static ErrorOr<Handle> create(Backend backend, int deviceId) { return open(backend, deviceId, 0, false); }
+  // A device (and a stream) can be chosen on the device backend only; on any other backend both
+  // overloads are InvalidArgument, as in the reference (handle.h:74-98).
+  static ErrorOr<Handle> create(Backend backend, int deviceId) {
+    FUSILLI_RETURN_ERROR_IF(backend != Backend::CUDA, ErrorCode::InvalidArgument,
+                            "Stream can only be set on the CUDA backend");
+    return open(backend, deviceId, 0, false);
+  }
   // `stream` is a cudaStream_t owned by the caller; work is enqueued on it and never
   // synchronised except by Buffer::read.
   static ErrorOr<Handle> create(Backend backend, int deviceId, uintptr_t stream) {

@@ -9,10 +9,14 @@
 
 #include <catch2/catch_test_macros.hpp>
 
+#include <atomic>
+#include <barrier>
 #include <cmath>
 #include <cstdint>
 #include <memory>
+#include <mutex>
 #include <random>
+#include <thread>
 #include <vector>
 
 using namespace fusilli;
@@ -279,4 +283,36 @@ TEST_CASE("one plan with a dynamic batch serves channels-last buffers of several
   auto st = g.execute(handle, pack, wsBuf);
   REQUIRE(st.getCode() == ErrorCode::InvalidArgument);
   REQUIRE(st.getMessage().find("imply") != std::string::npos);
+}
+
+TEST_CASE("32 threads create handles at once; deviceId / stream on the CPU backend is an InvalidArgument", "[handle]") {
+  // the reference's tests/test_handle.cpp:47-85, on the one backend that exists here
+  constexpr int kNumThreads = 32;
+  std::vector<std::thread> threads;
+  std::vector<Handle> handles;
+  handles.reserve(kNumThreads);
+  std::barrier startBarrier(kNumThreads);
+  std::atomic<bool> creationFailed{false};
+  std::mutex handlesMutex;
+  for (int i = 0; i < kNumThreads; ++i) {
+    threads.emplace_back([&]() {
+      startBarrier.arrive_and_wait();
+      auto h = Handle::create(kDefaultBackend);
+      if (isError(h)) {
+        creationFailed.store(true);
+        return;
+      }
+      std::lock_guard<std::mutex> lock(handlesMutex);
+      handles.push_back(std::move(*h));
+    });
+  }
+  for (auto &t : threads) t.join();
+  REQUIRE(!creationFailed.load());
+  REQUIRE(handles.size() == size_t(kNumThreads));
+  auto withStream = Handle::create(Backend::CPU, /*deviceId=*/0, /*stream=*/0);
+  REQUIRE(isError(withStream));
+  REQUIRE(ErrorObject(withStream).getCode() == ErrorCode::InvalidArgument);
+  auto withDevice = Handle::create(Backend::CPU, /*deviceId=*/0);
+  REQUIRE(isError(withDevice));
+  REQUIRE(ErrorObject(withDevice).getCode() == ErrorCode::InvalidArgument);
 }

@@ -7,7 +7,9 @@
 // and X's patch shifted by the tap offset [64 pixels][c] is the B tile, each fetched by
 // tiled 4-D TMA with zero fill outside the image (= the padding, and the ragged edge of
 // the pixel space). The A patch is loaded once and reused for every tap of the CTA's tap
-// group; each tap accumulates into its own TMEM columns (taps x BN <= 512).
+// group; each tap accumulates into its own TMEM columns (taps x BN <= 512). On narrow layers
+// (BN <= 128) the shifted X boxes of up to 256 / BN taps land side by side in one B stage and are
+// one MMA operand, N = taps x BN, writing those taps' adjacent column ranges at once.
 // The pixel reduction is split across CTAs: a CTA owns (ko tile, c tile, tap group, pixel
 // slice), writes its fp32 partial filter to the workspace, and a second kernel adds the
 // slices in a fixed order and converts -- deterministic, no atomics.
@@ -38,6 +40,7 @@ struct WgradTcParams {
   int32_t bw, bh, bn, tiles_w, tiles_h, tiles_nb;
   int32_t patches_total, patches_per_slice, slices;
   int32_t k_tiles, c_tiles, ngroups, taps_per_group, BN, a_halves;
+  int32_t tpack;            // filter taps that share one B stage and one MMA (tpack * BN <= 256)
   float *partial;           // [slices][Kout][R*S][C] fp32
   uint32_t *err;
 };
@@ -105,19 +108,24 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
       pha ^= (sa_i == 0);
       int ts = ts0, tr = tr0;
-      for (int t = 0; t < ntaps; ++t) {
+      // a stage takes the shifted X boxes of up to tpack taps side by side: they become the
+      // column blocks of ONE B operand, so narrow layers issue a quarter of the MMAs
+      for (int t = 0; t < ntaps; t += p.tpack) {
+        const int nt = min(p.tpack, ntaps - t);
         if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        mbar_expect_tx_elect(b_full(sb_i), b_bytes);
+        mbar_expect_tx_elect(b_full(sb_i), (uint32_t)nt * b_bytes);
         const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
-        for (int i = 0; i < p.BN / 64; ++i)
-          tma_load_4d_elect(sb + i * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i, w0 - p.pad_w + ts * p.dil_w,
-                            h0 - p.pad_h + tr * p.dil_h, n0);
+        for (int u = 0; u < nt; ++u) {
+          for (int i = 0; i < p.BN / 64; ++i)
+            tma_load_4d_elect(sb + (u * (p.BN / 64) + i) * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i,
+                              w0 - p.pad_w + ts * p.dil_w, h0 - p.pad_h + tr * p.dil_h, n0);
+          if (++ts == p.S) {
+            ts = 0;
+            ++tr;
+          }
+        }
         sb_i = (sb_i + 1 == B_STAGES) ? 0 : sb_i + 1;
         phb ^= (sb_i == 0);
-        if (++ts == p.S) {
-          ts = 0;
-          ++tr;
-        }
       }
       if (++tw == p.tiles_w) {
         tw = 0;
@@ -130,7 +138,10 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   } else if (warp == 1) {
     // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
     // elected lane issues the MMAs and the commits, which track the issuing thread.
-    const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 1, 1);
+    // one instruction descriptor per number of taps in a stage (N = taps * BN)
+    uint32_t idesc_n[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) idesc_n[u] = make_idesc_f16(BM, min((u + 1) * p.BN, MAX_BN), p.ab_format, 1, 1);
     // both tiles MN-major: 64-channel blocks HALF apart (LBO), 8-pixel groups 1024 B apart,
     // a 16-pixel K step is 2048 B
     const uint64_t a_desc0 = make_smem_desc(smem_base, HALF, 1024);
@@ -141,7 +152,9 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
     for (int pi = 0; pi < npatch && ok; ++pi) {
       if (!mbar_wait_warp(a_full(sa_i), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
       const uint64_t ad = a_desc0 + (uint64_t)((sa_i * A_STAGE_BYTES) >> 4);
-      for (int t = 0; t < ntaps; ++t) {
+      for (int t = 0; t < ntaps; t += p.tpack) {
+        const int nt = min(p.tpack, ntaps - t);
+        const uint32_t idesc = nt == 1 ? idesc_n[0] : (nt == 2 ? idesc_n[1] : (nt == 3 ? idesc_n[2] : idesc_n[3]));
         if (!mbar_wait_warp(b_full(sb_i), phb, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint64_t bd = b_desc0 + (uint64_t)((sb_i * B_STAGE_BYTES) >> 4);
@@ -337,6 +350,7 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
   p.k_tiles = t.k_tiles; p.c_tiles = t.c_tiles; p.ngroups = t.ngroups; p.taps_per_group = t.taps_per_group;
   p.BN = t.BN;
   p.a_halves = (v.Kout - 0 > 64) ? 2 : 1;
+  p.tpack = std::max(1, std::min(4, MAX_BN / t.BN));
   p.partial = reinterpret_cast<float *>(cx.workspace + s.scratch_offset);
   p.err = cx.dev->error_word;
   CUtensorMap tmDy, tmX;

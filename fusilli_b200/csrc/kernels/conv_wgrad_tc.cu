@@ -298,7 +298,10 @@ void wgrad_tiling(const WgradView &v, WgradTiling &t) {
   t.taps_per_group = (taps + t.ngroups - 1) / t.ngroups;
   t.ngroups = (taps + t.taps_per_group - 1) / t.taps_per_group;
   const int units = t.k_tiles * t.c_tiles * t.ngroups;
-  int slices = std::max(1, (2 * 148) / units);
+  // One CTA per SM: with two per SM (which run one after the other: shared memory and TMEM admit
+  // one) every layer was 7-15 % slower, each CTA paying its own prologue, first-load latency and
+  // accumulator drain, and the slice reduction reading twice the partials.
+  int slices = std::max(1, 148 / units);
   slices = std::min(slices, std::max(1, t.patches / 8));
   t.per_slice = (t.patches + slices - 1) / slices;
   t.slices = (t.patches + t.per_slice - 1) / t.per_slice;

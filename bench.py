@@ -100,6 +100,8 @@ class ClockSampler:
 def cpu_matmul_sample(rows: int, threads: int | None = None):
     """Oracle (CPU restatement) on `rows` rows of one 4096x4096x4096 product."""
     from oracle import fusilli_oracle as orc
+    # every host core, also under a launcher that exports OMP_NUM_THREADS=1 to its ranks
+    orc.set_threads(threads or os.cpu_count() or 1)
     rng = np.random.default_rng(0x5EED + 1)
     a = orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(rng.normal(0, 0.02, (rows, K)).astype(np.float32)))
     b = orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(rng.normal(0, 0.02, (K, N)).astype(np.float32)))

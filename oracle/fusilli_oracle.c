@@ -26,7 +26,25 @@
 
 #include "../include/fusilli_b200.h"
 
+
 #define ORC_API __attribute__((visibility("default")))
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Threads the loops below use. A launcher may export OMP_NUM_THREADS=1 to every process it starts
+ * (torchrun does); a caller that owns the host for the duration of a timing asks for the cores
+ * here instead. Returns the count in force. */
+ORC_API int orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 /* ---------------------------------------------------------------------- */
 /* Convolution. Dims are always given for three spatial axes (leading axes of */

@@ -49,6 +49,14 @@ def lib():
     return _lib
 
 
+def set_threads(n: int) -> int:
+    """OpenMP threads of the C kernels (overrides an inherited OMP_NUM_THREADS); returns the count."""
+    f = lib().orc_set_threads
+    f.restype = ctypes.c_int
+    f.argtypes = [ctypes.c_int]
+    return int(f(int(n)))
+
+
 # ---- dtype helpers -----------------------------------------------------------
 NP_DTYPE = {
     DataType.Half: np.float16, DataType.BFloat16: np.uint16, DataType.Float: np.float32,

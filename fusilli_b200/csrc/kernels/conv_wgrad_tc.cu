@@ -90,35 +90,58 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  if (warp == 0) {
-    // Whole warp in the loop, every issue predicated on an in-line election: coordinates stay in
-    // uniform registers and the tap counters advance without divisions.
-    int sa_i = 0, sb_i = 0;
-    uint32_t pha = 0, phb = 0;
-    bool ok = true;
-    const int ts0 = tap0 % p.S, tr0 = tap0 / p.S;
+  // Three warps feed the rings, each with its own copy of the patch and tap counters: one loads
+  // the dY patches, two take alternate B stages. A single producer warp was the pace of the whole
+  // kernel: every elected wait / expect / TMA issue costs it 100-300 clk one after the other
+  // (1113 clk per 64-pixel patch on a 1x1 layer that needs two boxes), while the MMA warp waited.
+  // Whole warp in the loop, every issue predicated on an in-line election: coordinates stay in
+  // uniform registers and the tap counters advance without divisions.
+  auto produce_a = [&]() {
+    int sa_i = 0;
+    uint32_t pha = 0;
     int tw = patch0 % p.tiles_w, th = (patch0 / p.tiles_w) % p.tiles_h, tb = patch0 / (p.tiles_w * p.tiles_h);
-    for (int pi = 0; pi < npatch && ok; ++pi) {
+    for (int pi = 0; pi < npatch; ++pi) {
       const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn;
-      if (!mbar_wait_warp(a_empty(sa_i), pha ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+      if (!mbar_wait_warp(a_empty(sa_i), pha ^ 1, p.err, ERR_WAIT_EMPTY)) break;
       mbar_expect_tx_elect(a_full(sa_i), a_bytes);
       const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
       for (int hh = 0; hh < p.a_halves; ++hh)
         tma_load_4d_elect(sa + hh * HALF, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
       sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
       pha ^= (sa_i == 0);
+      if (++tw == p.tiles_w) {
+        tw = 0;
+        if (++th == p.tiles_h) {
+          th = 0;
+          ++tb;
+        }
+      }
+    }
+  };
+  auto produce_b = [&](int parity) {
+    int sb_i = 0, chunk = 0;
+    uint32_t phb = 0;
+    bool ok = true;
+    const int ts0 = tap0 % p.S, tr0 = tap0 / p.S;
+    int tw = patch0 % p.tiles_w, th = (patch0 / p.tiles_w) % p.tiles_h, tb = patch0 / (p.tiles_w * p.tiles_h);
+    for (int pi = 0; pi < npatch && ok; ++pi) {
+      const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn;
       int ts = ts0, tr = tr0;
       // a stage takes the shifted X boxes of up to tpack taps side by side: they become the
       // column blocks of ONE B operand, so narrow layers issue a quarter of the MMAs
-      for (int t = 0; t < ntaps; t += p.tpack) {
+      for (int t = 0; t < ntaps; t += p.tpack, ++chunk) {
         const int nt = min(p.tpack, ntaps - t);
-        if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        mbar_expect_tx_elect(b_full(sb_i), (uint32_t)nt * b_bytes);
+        const bool mine = (chunk & 1) == parity;
+        if (mine) {
+          if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx_elect(b_full(sb_i), (uint32_t)nt * b_bytes);
+        }
         const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
         for (int u = 0; u < nt; ++u) {
-          for (int i = 0; i < p.BN / 64; ++i)
-            tma_load_4d_elect(sb + (u * (p.BN / 64) + i) * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i,
-                              w0 - p.pad_w + ts * p.dil_w, h0 - p.pad_h + tr * p.dil_h, n0);
+          if (mine)
+            for (int i = 0; i < p.BN / 64; ++i)
+              tma_load_4d_elect(sb + (u * (p.BN / 64) + i) * HALF, &tmap_x, b_full(sb_i), ct * p.BN + 64 * i,
+                                w0 - p.pad_w + ts * p.dil_w, h0 - p.pad_h + tr * p.dil_h, n0);
           if (++ts == p.S) {
             ts = 0;
             ++tr;
@@ -135,6 +158,10 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
         }
       }
     }
+  };
+
+  if (warp == 0) {
+    produce_b(0);
   } else if (warp == 1) {
     // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
     // elected lane issues the MMAs and the commits, which track the issuing thread.
@@ -172,6 +199,9 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
     }
     if (ok) tc_commit_elect(acc_full);
   } else {
+    if (warp == 2) produce_a();
+    if (warp == 3) produce_b(1);
+    __syncwarp();
     const int q = warp & 3;
     const int ko = kt * BM + q * 32 + lane;
     const int taps_all = p.R * p.S;

@@ -30,6 +30,7 @@ constexpr int B_STAGE_BYTES = MAX_BN * KPIX * 2; // 32 KB
 constexpr int HALF = 64 * KPIX * 2;              // one [64 pixels][64 channels] box
 constexpr int SMEM_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 256;
 constexpr int NUM_THREADS = 192;
+constexpr int B_PRODUCERS = 4; // warps 0, 3, 4, 5 take every fourth B stage each
 constexpr int TMEM_COLS = 512;
 
 struct WgradTcParams {
@@ -118,7 +119,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       }
     }
   };
-  auto produce_b = [&](int parity) {
+  auto produce_b = [&](int id) {
     int sb_i = 0, chunk = 0;
     uint32_t phb = 0;
     bool ok = true;
@@ -131,7 +132,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       // column blocks of ONE B operand, so narrow layers issue a quarter of the MMAs
       for (int t = 0; t < ntaps; t += p.tpack, ++chunk) {
         const int nt = min(p.tpack, ntaps - t);
-        const bool mine = (chunk & 1) == parity;
+        const bool mine = (chunk & (B_PRODUCERS - 1)) == id;
         if (mine) {
           if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
           mbar_expect_tx_elect(b_full(sb_i), (uint32_t)nt * b_bytes);
@@ -200,7 +201,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
     if (ok) tc_commit_elect(acc_full);
   } else {
     if (warp == 2) produce_a();
-    if (warp == 3) produce_b(1);
+    if (warp >= 3) produce_b(warp - 2);
     __syncwarp();
     const int q = warp & 3;
     const int ko = kt * BM + q * 32 + lane;

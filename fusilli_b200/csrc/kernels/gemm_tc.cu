@@ -33,7 +33,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 224; // TMA warp, MMA warp, 4 epilogue warps, second TMA warp
+constexpr int PRODUCERS = 2;
 constexpr int TMEM_COLS = 512;
 
 struct GemmTcParams {
@@ -108,7 +109,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int kblocks = (p.K + BK - 1) / BK;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
+    // Two producer warps take alternate K blocks: waits, expect and the TMA issues of one block
+    // are a serial chain of long-latency instructions in the issuing thread.
+    const uint32_t pid = warp == 0 ? 0u : 1u;
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -116,6 +120,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const WorkItem wi = decode_work(p, w);
         const int m0 = wi.m0, n0 = wi.n0, b = wi.b, nb = wi.nb;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((it % PRODUCERS) != pid) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }

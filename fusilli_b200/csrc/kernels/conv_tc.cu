@@ -113,7 +113,9 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint3
   }
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// The per-tap kernel runs one more warp than the halo kernel: a second TMA producer.
+constexpr int NUM_THREADS_TAP = NUM_THREADS + 32;
+__global__ void __launch_bounds__(NUM_THREADS_TAP, 1)
 conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -154,9 +156,14 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int kblocks = p.R * p.S * p.cblocks;
   const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
 
-  if (warp == 0) {
-    // Whole warp in the loop, one elected lane issues: coordinates and addresses stay in uniform
-    // registers, and the channel-block / tap counters advance without divisions.
+  if (warp == 0 || warp == NUM_THREADS / 32) {
+    // Two producer warps take alternate K blocks (the wait, the expect and the TMA issues of a
+    // block are a serial chain of long-latency instructions in the issuing warp; one warp set the
+    // pace of the kernel on narrow layers). Both run the whole loop so that slot, phase and tap
+    // counters stay in step; whole warp in the loop, one elected lane issues: coordinates and
+    // addresses stay in uniform registers, the counters advance without divisions.
+    const uint32_t pid = warp == 0 ? 0u : 1u;
+    uint32_t it = 0;
     const bool leader = elect_one();
     int s = 0;       // ring slot and its phase, advanced together (the depth is a run-time value)
     uint32_t ph = 0;
@@ -167,19 +174,21 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
       const int w0 = tw * p.bw + p.off_w, h0 = th * p.bh + p.off_h, n0 = tb * p.bn, no0 = tno * p.BN;
       int cb = 0, ts = 0, tr = 0; // channel block (fastest), filter column, filter row
-      for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
-        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + A_BYTES;
-        const int c0 = cb * BK;
-        mbar_expect_tx_elect(full_bar(s), p.a_bytes + p.b_bytes);
-        tma_load_4d_elect(sa, &tmap_a, full_bar(s), c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
-        if (!p.dgrad) {
-          // filter rows ko, contraction channel c contiguous: one K-major box
-          tma_load_4d_elect(sb, &tmap_b, full_bar(s), c0, ts, tr, no0);
-        } else {
-          // filter rows ko (contraction), output channel c contiguous: MN-major 64-wide blocks
-          for (int i = 0; i < p.BN / 64; ++i)
-            tma_load_4d_elect(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), no0 + 64 * i, ts, tr, c0);
+      for (int kb = 0; kb < kblocks; ++kb, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+        if ((it & 1u) == pid) {
+          if (!mbar_wait_warp(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + A_BYTES;
+          const int c0 = cb * BK;
+          mbar_expect_tx_elect(full_bar(s), p.a_bytes + p.b_bytes);
+          tma_load_4d_elect(sa, &tmap_a, full_bar(s), c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
+          if (!p.dgrad) {
+            // filter rows ko, contraction channel c contiguous: one K-major box
+            tma_load_4d_elect(sb, &tmap_b, full_bar(s), c0, ts, tr, no0);
+          } else {
+            // filter rows ko (contraction), output channel c contiguous: MN-major 64-wide blocks
+            for (int i = 0; i < p.BN / 64; ++i)
+              tma_load_4d_elect(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), no0 + 64 * i, ts, tr, c0);
+          }
         }
         if (++cb == p.cblocks) {
           cb = 0;
@@ -637,7 +646,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     conv_halo_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
     return FB_OK;
   }
-  conv_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+  conv_tcgen05_kernel<<<grid, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
   return FB_OK;
 }
 

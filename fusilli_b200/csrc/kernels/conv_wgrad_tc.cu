@@ -246,12 +246,38 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   }
 }
 
-// out[i] = sum over slices of partial[s][i], slice order fixed.
+// out[i] = sum over slices of partial[s][i] in a fixed order: four threads per element take every
+// fourth slice each (eight loads in flight per thread: one dependent load per slice made this pass
+// latency-bound) and their sums are combined pairwise, (g0 + g1) + (g2 + g3).
 __global__ void __launch_bounds__(256)
 wgrad_slice_reduce_kernel(const float *__restrict__ partial, void *out, int out_dtype, int64_t elems, int slices) {
+  const int g = threadIdx.x & 3;
+  const int64_t per_block = blockDim.x / 4;
+  for (int64_t i0 = (int64_t)blockIdx.x * per_block; i0 < elems; i0 += (int64_t)gridDim.x * per_block) {
+    const int64_t i = i0 + (threadIdx.x >> 2);
+    float acc = 0.f;
+    if (i < elems) {
+      int s = g;
+      for (; s + 28 < slices; s += 32) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = __ldg(partial + (int64_t)(s + 4 * u) * elems + i);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += v[u];
+      }
+      for (; s < slices; s += 4) acc += __ldg(partial + (int64_t)s * elems + i);
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (g == 0 && i < elems) store_f(out, out_dtype, i, acc);
+  }
+}
+
+// The same with one thread per element: few slices and a large filter (coalesced rows, nothing to
+// spread).
+__global__ void __launch_bounds__(256)
+wgrad_slice_reduce1_kernel(const float *__restrict__ partial, void *out, int out_dtype, int64_t elems, int slices) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (int64_t)gridDim.x * blockDim.x) {
-    // eight loads in flight, added in slice order: one dependent load per slice made this pass
-    // latency-bound (20 us for 21 MB of partials)
     float acc = 0.f;
     int s = 0;
     for (; s + 8 <= slices; s += 8) {
@@ -407,8 +433,13 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
              std::string("conv_wgrad_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
   const int grid = t.k_tiles * t.c_tiles * t.ngroups * t.slices;
   conv_wgrad_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmDy, tmX, p);
-  const int rblocks = (int)std::min<int64_t>((elems + 255) / 256, (int64_t)cx.dev->sm_count * 8);
-  wgrad_slice_reduce_kernel<<<rblocks, 256, 0, cx.dev->stream>>>(p.partial, dwp, dw.dtype, elems, t.slices);
+  if (t.slices >= 16) {
+    const int rblocks = (int)std::min<int64_t>((elems + 63) / 64, (int64_t)cx.dev->sm_count * 8);
+    wgrad_slice_reduce_kernel<<<rblocks, 256, 0, cx.dev->stream>>>(p.partial, dwp, dw.dtype, elems, t.slices);
+  } else {
+    const int rblocks = (int)std::min<int64_t>((elems + 255) / 256, (int64_t)cx.dev->sm_count * 8);
+    wgrad_slice_reduce1_kernel<<<rblocks, 256, 0, cx.dev->stream>>>(p.partial, dwp, dw.dtype, elems, t.slices);
+  }
   return FB_OK;
 }
 

@@ -439,9 +439,9 @@ def run_ours(args):
                        "parallelism": f"batch sharded over {world} GPU(s), no data-path collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["tf_burst"], "unit": "TFLOP/s",
                          "frac": achieved / pk["tf_burst"],
-                         # dram__bytes_read+write of one ncu capture at 2 x 4096^3 (207.9 MB,
+                         # dram__bytes_read+write of one ncu capture at 2 x 4096^3 (206.6 MB,
                          # profiles/gemm_tcgen05_c2.md), scaled by the matrices one launch processes
-                         "traffic": 207.9e6 * b_local / 2, "traffic_algorithmic": 3.0 * b_local * M * N * 2,
+                         "traffic": 206.6e6 * b_local / 2, "traffic_algorithmic": 3.0 * b_local * M * N * 2,
                          "peak_source": pk["source"],
                          "kernel": "gemm_tcgen05_kernel", "kernel_ms": kern_ms,
                          "frac_of_sustained": achieved / pk["tf_sustained"]},

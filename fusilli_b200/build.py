@@ -14,6 +14,7 @@ OBJ = os.path.join(HERE, "_obj")
 
 SOURCES = [
     "runtime.cu",
+    "comm.cu",
     "plan.cpp",
     "kernels/pointwise.cu",
     "kernels/reduce.cu",
@@ -25,6 +26,7 @@ SOURCES = [
     "kernels/conv_tc.cu",
     "kernels/conv_wgrad_tc.cu",
     "kernels/sdpa_tc.cu",
+    "kernels/selftest.cu",
 ]
 
 NVCC_FLAGS = [

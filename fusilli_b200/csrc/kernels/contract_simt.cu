@@ -38,7 +38,7 @@ struct ContractParams {
   int64_t M, N, K, k_chunk;
   // matmul addressing
   int32_t nbatch_dims;
-  int64_t bdims[6], a_bstr[6], b_bstr[6], c_bstr[6];
+  int64_t bdims[6], a_bdims[6], b_bdims[6], a_bstr[6], b_bstr[6], c_bstr[6];
   int64_t a_sm, a_sk, b_sk, b_sn, c_sm, c_sn;
   ConvGeomDev g;
   EpilogueDev epi;
@@ -53,8 +53,10 @@ __device__ __forceinline__ void batch_offsets(const ContractParams &p, int g, in
   for (int d = p.nbatch_dims - 1; d >= 0; --d) {
     int c = rem % (int)p.bdims[d];
     rem /= (int)p.bdims[d];
-    ao += c * p.a_bstr[d];
-    bo += c * p.b_bstr[d];
+    // an operand whose batch dim divides the result's is read modulo (reference
+    // matmul_node.h:140-150 accepts such dims; 1 is the usual broadcast)
+    ao += (c % (int)p.a_bdims[d]) * p.a_bstr[d];
+    bo += (c % (int)p.b_bdims[d]) * p.b_bstr[d];
     co += c * p.c_bstr[d];
     if (idx) idx[d] = c;
   }
@@ -463,11 +465,10 @@ fb_status launch_contract_simt(const ExecContext &cx, const Step &s) {
       p.bdims[i] = to.dims[i];
       p.a_bstr[i] = t0.dims[i] == 1 ? 0 : t0.strides[i];
       p.b_bstr[i] = t1.dims[i] == 1 ? 0 : t1.strides[i];
-      // partial broadcast (dim divides) is index modulo: only exact or 1 handled here
-      FB_REQUIRE(t0.dims[i] == to.dims[i] || t0.dims[i] == 1, FB_NOT_IMPLEMENTED,
-                 "matmul: batch broadcast of A by a proper divisor is not supported");
-      FB_REQUIRE(t1.dims[i] == to.dims[i] || t1.dims[i] == 1, FB_NOT_IMPLEMENTED,
-                 "matmul: batch broadcast of B by a proper divisor is not supported");
+      p.a_bdims[i] = t0.dims[i];
+      p.b_bdims[i] = t1.dims[i];
+      FB_REQUIRE(to.dims[i] % t0.dims[i] == 0 && to.dims[i] % t1.dims[i] == 0, FB_INVALID_ARGUMENT,
+                 "matmul: a batch dim of an operand does not divide the result's");
       p.c_bstr[i] = tc.strides[i];
       G *= to.dims[i];
     }
@@ -585,9 +586,13 @@ __device__ __align__(256) float g_wgrad_static_scratch[kStaticScratchBytes / siz
 constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 float *g_static_scratch_ptr[kMaxDevices] = {nullptr};
+int g_static_sm_count[kMaxDevices] = {0};
 
-// Device address of the scratch array on the CURRENT device (resolved on first use).
-fb_status static_scratch_for_current_device(float **out) {
+// Device address of the scratch array on the CURRENT device and that device's SM count, both
+// resolved on the first call per device. That first call may make the CUDA runtime load this
+// library's device code onto the GPU (and so allocate): it belongs outside any region where
+// allocation is forbidden, and before any stream capture.
+fb_status static_scratch_for_current_device(float **out, int *sm_count) {
   int dev = -1;
   FB_CUDA_OK(cudaGetDevice(&dev));
   FB_REQUIRE(dev >= 0 && dev < kMaxDevices, FB_RUNTIME_FAILURE, "device ordinal out of range");
@@ -598,9 +603,15 @@ fb_status static_scratch_for_current_device(float **out) {
     if (e != cudaSuccess || p == nullptr)
       return fail(FB_RUNTIME_FAILURE,
                   std::string("cudaGetSymbolAddress(static wgrad scratch): ") + cudaGetErrorString(e));
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || sms <= 0)
+      return fail(FB_RUNTIME_FAILURE, std::string("cudaDeviceGetAttribute(SM count): ") + cudaGetErrorString(e));
+    g_static_sm_count[dev] = sms;
     g_static_scratch_ptr[dev] = static_cast<float *>(p);
   }
   *out = g_static_scratch_ptr[dev];
+  *sm_count = g_static_sm_count[dev];
   return FB_OK;
 }
 
@@ -631,9 +642,13 @@ FB_EXPORT fb_status fb_conv_wgrad_static(void *stream, const void *dy, const voi
   const int64_t red = (int64_t)n * oh * ow;
   FB_REQUIRE(red < (1ll << 31) && dw_elems < (1ll << 31), FB_NOT_IMPLEMENTED,
              "fb_conv_wgrad_static: problem extent exceeds 2^31");
+  float *scratch = nullptr;
+  int sms = 0;
+  fb_status st = static_scratch_for_current_device(&scratch, &sms);
+  if (st != FB_OK) return st;
   // Same split heuristic as the planned path, then capped by the fixed scratch.
   const int64_t tiles = ((kg + BM - 1) / BM) * ((cg * r * s + BN - 1) / BN) * groups;
-  int64_t split = (2 * 148 + tiles - 1) / tiles;
+  int64_t split = (2 * sms + tiles - 1) / tiles;
   split = std::min<int64_t>(split, std::max<int64_t>(red / 256, 1));
   split = std::min<int64_t>(split, 64);
   const int64_t max_split = (int64_t)(kStaticScratchBytes / sizeof(float)) / dw_elems;
@@ -642,10 +657,6 @@ FB_EXPORT fb_status fb_conv_wgrad_static(void *stream, const void *dy, const voi
                  " bytes (fp32) exceeds the static scratch of " + std::to_string(kStaticScratchBytes) +
                  " bytes; use the planned path with a caller-provided workspace");
   split = std::max<int64_t>(1, std::min(split, max_split));
-
-  float *scratch = nullptr;
-  fb_status st = static_scratch_for_current_device(&scratch);
-  if (st != FB_OK) return st;
 
   static thread_local ContractParams p;
   memset(&p, 0, sizeof(p));
@@ -684,7 +695,7 @@ FB_EXPORT fb_status fb_conv_wgrad_static(void *stream, const void *dy, const voi
   contract_simt_kernel<<<grid, 256, 0, cs>>>(p);
   if (p.split_k > 1) {
     int64_t total = (int64_t)p.G * p.M * p.N;
-    int blocks = (int)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)sms * 8);
     contract_splitk_reduce_kernel<<<blocks, 256, 0, cs>>>(p);
   }
   cudaError_t le = cudaGetLastError();

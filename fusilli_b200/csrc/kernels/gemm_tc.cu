@@ -40,7 +40,7 @@ constexpr int TMEM_COLS = 512;
 struct GemmTcParams {
   int32_t M, N, K, batches;
   int32_t a_mn_major, b_mn_major;
-  int32_t a_batch_mul, b_batch_mul;
+  int32_t a_batches, b_batches; // distinct matrices of each operand: batch b reads matrix b % count
   int32_t ab_format;
   int32_t tiles_m, tiles_n, total_tiles;
   // Work items: tiles [0, full_tiles) whole, the rest as two 128-column halves each. The host
@@ -118,7 +118,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       bool ok = true;
       for (int w = blockIdx.x; w < p.total_work && ok; w += gridDim.x) {
         const WorkItem wi = decode_work(p, w);
-        const int m0 = wi.m0, n0 = wi.n0, b = wi.b, nb = wi.nb;
+        const int m0 = wi.m0, n0 = wi.n0, nb = wi.nb;
+        const int ba = wi.b % p.a_batches, bb = wi.b % p.b_batches;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           if ((it % PRODUCERS) != pid) continue;
           const int s = it % STAGES;
@@ -128,23 +129,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
           const int k0 = kb * BK;
           if (!p.a_mn_major) {
-            tma_load_3d(sa, &tmap_a, full_bar(s), k0, m0, b * p.a_batch_mul);
+            tma_load_3d(sa, &tmap_a, full_bar(s), k0, m0, ba);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i)
-              tma_load_3d(sa + i * (64 * BK * 2), &tmap_a, full_bar(s), m0 + 64 * i, k0, b * p.a_batch_mul);
+              tma_load_3d(sa + i * (64 * BK * 2), &tmap_a, full_bar(s), m0 + 64 * i, k0, ba);
           }
           if (!p.b_mn_major) {
             // boxes of BN / 2 rows: one per half
 #pragma unroll
             for (int i = 0; i < 2; ++i)
               if (i * (BN / 2) < nb)
-                tma_load_3d(sb + i * ((BN / 2) * BK * 2), &tmap_b, full_bar(s), k0, n0 + (BN / 2) * i, b * p.b_batch_mul);
+                tma_load_3d(sb + i * ((BN / 2) * BK * 2), &tmap_b, full_bar(s), k0, n0 + (BN / 2) * i, bb);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i)
               if (i * 64 < nb)
-                tma_load_3d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), n0 + 64 * i, k0, b * p.b_batch_mul);
+                tma_load_3d(sb + i * (64 * BK * 2), &tmap_b, full_bar(s), n0 + 64 * i, k0, bb);
           }
         }
       }
@@ -294,25 +295,36 @@ struct GemmView {
   int a_mn, b_mn;      // operand is MN-major
   int64_t a_ld, b_ld;  // leading (slow) stride in elements
   int64_t a_bs, b_bs;  // batch strides (0 = broadcast)
+  int64_t a_nb, b_nb;  // distinct matrices of A and B (1 = broadcast; a divisor of `batches` otherwise)
   int64_t ldc, c_bs;
 };
 
 bool is16(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16; }
 bool isfl(int dt) { return dt == FB_DT_HALF || dt == FB_DT_BFLOAT16 || dt == FB_DT_FLOAT; }
 
-// Collapses the batch dims of `t` into (count, stride); false if they are not a
-// dense run (or a pure broadcast).
-bool batch_collapse(const TensorInfo &t, const TensorInfo &full, int64_t &stride) {
+// Collapses the batch dims of `t` into (count, stride): `count` distinct matrices `stride` elements
+// apart, batch b of the result reading matrix b % count. False if the batch dims are not a dense
+// run, a pure broadcast, or (single batch dim only) a proper divisor of the result's batch
+// (reference matmul_node.h:140-150 accepts dims that divide one another).
+bool batch_collapse(const TensorInfo &t, const TensorInfo &full, int64_t &stride, int64_t &count) {
   int nb = t.rank - 2;
   bool all_one = true;
-  for (int i = 0; i < nb; ++i)
+  count = 1;
+  for (int i = 0; i < nb; ++i) {
     if (t.dims[i] != 1) all_one = false;
+    count *= t.dims[i];
+  }
   if (all_one) {
     stride = 0;
     return true;
   }
+  if (nb == 1 && t.dims[0] != full.dims[0]) {
+    if (full.dims[0] % t.dims[0] != 0) return false;
+    stride = t.strides[0];
+    return true;
+  }
   for (int i = 0; i < nb; ++i)
-    if (t.dims[i] != full.dims[i]) return false; // partial broadcast
+    if (t.dims[i] != full.dims[i]) return false; // partial broadcast over several batch dims
   int64_t expect = -1;
   for (int i = nb - 1; i >= 0; --i) {
     if (t.dims[i] == 1) continue;
@@ -346,8 +358,13 @@ bool gemm_view(const Plan &p, const Step &s, GemmView &g) {
   else return false;
   if (c.strides[r - 1] != 1) return false;
   g.ldc = c.strides[r - 2];
-  if (!batch_collapse(a, c, g.a_bs) || !batch_collapse(b, c, g.b_bs) || !batch_collapse(c, c, g.c_bs)) return false;
+  int64_t c_nb = 1;
+  if (!batch_collapse(a, c, g.a_bs, g.a_nb) || !batch_collapse(b, c, g.b_bs, g.b_nb) ||
+      !batch_collapse(c, c, g.c_bs, c_nb))
+    return false;
   if (g.batches == 1) g.a_bs = g.b_bs = g.c_bs = 0;
+  if (!g.a_bs) g.a_nb = 1;
+  if (!g.b_bs) g.b_nb = 1;
   // TMA: 16-byte aligned strides
   if (g.a_ld % 8 || g.b_ld % 8 || g.a_bs % 8 || g.b_bs % 8) return false;
   if (g.M >= (1ll << 31) || g.N >= (1ll << 31) || g.K >= (1ll << 31) || g.batches >= 65536) return false;
@@ -403,8 +420,8 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   memset(&p, 0, sizeof(p));
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.batches = (int)g.batches;
   p.a_mn_major = g.a_mn; p.b_mn_major = g.b_mn;
-  p.a_batch_mul = g.a_bs ? 1 : 0;
-  p.b_batch_mul = g.b_bs ? 1 : 0;
+  p.a_batches = (int)g.a_nb;
+  p.b_batches = (int)g.b_nb;
   p.ab_format = a.dtype == FB_DT_BFLOAT16 ? 1 : 0;
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
@@ -449,7 +466,7 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   const char *why = "";
   {
     // innermost-first dims; a broadcast operand gets a batch extent of 1
-    uint64_t ab = g.a_bs ? (uint64_t)g.batches : 1, bb = g.b_bs ? (uint64_t)g.batches : 1;
+    uint64_t ab = (uint64_t)g.a_nb, bb = (uint64_t)g.b_nb;
     uint64_t a_bstride = g.a_bs ? (uint64_t)g.a_bs * 2 : (uint64_t)g.a_ld * 2 * (g.a_mn ? g.K : g.M);
     uint64_t b_bstride = g.b_bs ? (uint64_t)g.b_bs * 2 : (uint64_t)g.b_ld * 2 * (g.b_mn ? g.K : g.N);
     if (!g.a_mn) {

@@ -8,8 +8,11 @@
 // conv+bias+relu, tests/lit/test_conv_asm_emitter_nhwc_krsc_with_relu.cpp:103-106).
 // Every other node is one kernel; virtual tensors that cross kernels live in the
 // caller-provided workspace.
+#include <algorithm>
 #include <cstring>
 #include <sstream>
+#include <utility>
+#include <vector>
 
 #include "common.h"
 
@@ -34,6 +37,20 @@ static bool same_dims(const TensorInfo &a, const TensorInfo &b) {
   for (int i = 0; i < a.rank; ++i)
     if (a.dims[i] != b.dims[i]) return false;
   return true;
+}
+
+// Dims 1.. form one dense block (in any order) and dim 0 strides over whole blocks.
+static bool dense_batch_outermost(const TensorInfo &t) {
+  std::vector<std::pair<int64_t, int64_t>> inner; // (stride, dim)
+  for (int i = 1; i < t.rank; ++i)
+    if (t.dims[i] > 1) inner.emplace_back(t.strides[i], t.dims[i]);
+  std::sort(inner.begin(), inner.end());
+  int64_t expect = 1;
+  for (const auto &sd : inner) {
+    if (sd.first != expect) return false;
+    expect *= sd.second;
+  }
+  return t.dims[0] == 1 || t.strides[0] == expect;
 }
 
 // `o` broadcasts (right aligned) to `full` without enlarging it.
@@ -77,17 +94,16 @@ static fb_status check_node(const Plan &p, int ni) {
                      " tensors is not supported (f16, bf16, f32; si4 operands)");
     }
     {
-      // The reference lets a batch dim of one operand divide the other's (matmul_node.h:140-150);
-      // the kernels broadcast a batch dim only from 1, and say so here rather than at execute.
+      // The reference lets a batch dim of one operand divide the other's (matmul_node.h:140-150):
+      // the smaller operand is read modulo its own extent.
       const TensorInfo &a = p.tensors[d.inputs[0]], &b = p.tensors[d.inputs[1]], &c = p.tensors[d.outputs[0]];
       FB_REQUIRE(a.rank >= 2 && a.rank == b.rank && a.rank == c.rank, FB_INVALID_ARGUMENT,
                  "node '" + nm + "': matmul tensors must have one rank >= 2");
       FB_REQUIRE(a.rank - 2 <= 6, FB_NOT_IMPLEMENTED, "node '" + nm + "': more than 6 matmul batch dims");
       for (int i = 0; i + 2 < a.rank; ++i)
-        FB_REQUIRE((a.dims[i] == c.dims[i] || a.dims[i] == 1) && (b.dims[i] == c.dims[i] || b.dims[i] == 1),
-                   FB_NOT_IMPLEMENTED,
+        FB_REQUIRE(c.dims[i] % a.dims[i] == 0 && c.dims[i] % b.dims[i] == 0, FB_INVALID_ARGUMENT,
                    "node '" + nm + "': matmul batch dim " + std::to_string(i) +
-                       " broadcasts by a proper divisor, which is not supported");
+                       " of an operand does not divide the result's");
     }
     return FB_OK;
   case FB_OP_SDPA:
@@ -113,6 +129,12 @@ static fb_status check_node(const Plan &p, int ni) {
                "node '" + nm + "': normalisation tensors must be f16, bf16 or f32");
     FB_REQUIRE(!(d.op == FB_OP_RMSNORM && (d.flags & FB_FLAG_NORM_TRAINING)), FB_NOT_IMPLEMENTED,
                "RmsNorm training forward phase is not implemented");
+    // The kernels walk a sample as one dense run of prod(dims[1:]) elements: X and Y must be dense
+    // with the batch dim outermost in memory (contiguous and channels-last both are).
+    for (int id : {d.inputs[0], d.outputs[0]})
+      FB_REQUIRE(dense_batch_outermost(p.tensors[id]), FB_NOT_IMPLEMENTED,
+                 "node '" + nm + "': tensor '" + p.tensors[id].name +
+                     "' must be dense with the batch dim outermost in memory");
     return FB_OK;
   }
   case FB_OP_BATCHNORM: {

@@ -40,11 +40,14 @@ const char *dtype_name(int32_t dt) {
   return (dt >= 0 && dt <= FB_DT_FP8E5M2) ? names[dt] : "?";
 }
 
+// Elements the buffer must hold: one past the offset of the last element. For a dense tensor in
+// any dim order this is the product of the dims; with padded strides (a matmul operand whose
+// leading stride exceeds its row length) it is larger, and the size check must see that.
 int64_t TensorInfo::phys_elems() const {
-  int64_t n = 1;
+  int64_t last = 0;
   for (int i = 0; i < rank; ++i)
-    if (strides[i] != 0) n *= dims[i];
-  return n;
+    if (strides[i] != 0) last += (dims[i] - 1) * strides[i];
+  return last + 1;
 }
 
 size_t TensorInfo::phys_bytes() const { return ((size_t)phys_elems() * dtype_bits(dtype) + 7) / 8; }
@@ -79,9 +82,10 @@ struct fb_plan {
   Plan plan;
   int ordinal = 0;
   // Plans lowered again for concrete extents of the dynamic dims, keyed by the extents of all
-  // arguments. Bounded: shapes past the limit replace the whole set.
+  // arguments. Bounded: shapes past the limit replace the whole set. Entries are shared: a caller
+  // holds its own reference for the length of its execute, so dropping the set under it is safe.
   std::mutex mu;
-  std::map<std::vector<int64_t>, std::unique_ptr<Plan>> shaped;
+  std::map<std::vector<int64_t>, std::shared_ptr<const Plan>> shaped;
   static constexpr size_t kMaxShaped = 64;
 };
 
@@ -530,7 +534,8 @@ FB_EXPORT fb_status fb_plan_execute(fb_plan *plan, fb_device *dev, void *const *
 }
 
 // The plan for these extents: the loaded one when they are its own, else a specialisation (kept).
-static fb_status shaped_plan(fb_plan *plan, const int64_t *arg_dims, int32_t num_args, const Plan **out) {
+static fb_status shaped_plan(fb_plan *plan, const int64_t *arg_dims, int32_t num_args,
+                             std::shared_ptr<const Plan> *out) {
   const Plan &base = plan->plan;
   FB_REQUIRE(num_args == base.num_args, FB_VARIANT_PACK_ERROR,
              "expected " + std::to_string(base.num_args) + " buffers, got " + std::to_string(num_args));
@@ -546,19 +551,20 @@ static fb_status shaped_plan(fb_plan *plan, const int64_t *arg_dims, int32_t num
     }
   }
   if (same) {
-    *out = &base;
+    // the loaded plan itself: aliasing pointer without ownership (it lives as long as `plan`)
+    *out = std::shared_ptr<const Plan>(std::shared_ptr<const Plan>(), &base);
     return FB_OK;
   }
   std::lock_guard<std::mutex> lock(plan->mu);
   auto it = plan->shaped.find(key);
   if (it == plan->shaped.end()) {
-    auto sp = std::make_unique<Plan>();
+    auto sp = std::make_shared<Plan>();
     fb_status st = specialize(base, arg_dims, *sp);
     if (st != FB_OK) return st;
     if (plan->shaped.size() >= fb_plan::kMaxShaped) plan->shaped.clear();
-    it = plan->shaped.emplace(std::move(key), std::move(sp)).first;
+    it = plan->shaped.emplace(std::move(key), std::shared_ptr<const Plan>(std::move(sp))).first;
   }
-  *out = it->second.get();
+  *out = it->second;
   return FB_OK;
 }
 
@@ -567,7 +573,7 @@ FB_EXPORT fb_status fb_plan_execute_shaped(fb_plan *plan, fb_device *dev, void *
                                            int32_t num_args, void *workspace, size_t workspace_bytes) {
   clear_error();
   FB_REQUIRE(plan && dev, FB_INVALID_ARGUMENT, "fb_plan_execute_shaped: NULL plan or device");
-  const Plan *p = nullptr;
+  std::shared_ptr<const Plan> p;
   fb_status st = shaped_plan(plan, arg_dims, num_args, &p);
   if (st != FB_OK) return st;
   return execute_plan(plan, *p, dev, args, arg_bytes, num_args, workspace, workspace_bytes);
@@ -577,7 +583,7 @@ FB_EXPORT fb_status fb_plan_workspace_size_shaped(fb_plan *plan, const int64_t *
                                                   size_t *bytes) {
   clear_error();
   FB_REQUIRE(plan && bytes, FB_INVALID_ARGUMENT, "fb_plan_workspace_size_shaped: NULL argument");
-  const Plan *p = nullptr;
+  std::shared_ptr<const Plan> p;
   fb_status st = shaped_plan(plan, arg_dims, num_args, &p);
   if (st != FB_OK) return st;
   *bytes = p->workspace_bytes;

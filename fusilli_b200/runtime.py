@@ -83,6 +83,20 @@ ABI_SYMBOLS = [
     ("fb_plan_specialize", _I32, [ctypes.c_char_p, _SZ, ctypes.POINTER(ctypes.c_int64), _I32,
                                   ctypes.POINTER(ctypes.POINTER(ctypes.c_uint8)), ctypes.POINTER(_SZ)]),
     ("fb_plan_workspace_size_shaped", _I32, [_VP, ctypes.POINTER(ctypes.c_int64), _I32, ctypes.POINTER(_SZ)]),
+    ("fb_device_selftest_wait_timeout", _I32, [_VP, ctypes.c_uint32, ctypes.c_uint32]),
+    ("fb_device_clear_kernel_error", _I32, [_VP]),
+    ("fb_comm_create", _I32, [_VP, _I32, _I32, _SZ, ctypes.POINTER(_VP)]),
+    ("fb_comm_local_handle", _I32, [_VP, ctypes.c_char_p]),
+    ("fb_comm_connect", _I32, [_VP, ctypes.c_char_p]),
+    ("fb_comm_close", _I32, [_VP]),
+    ("fb_comm_buffer", _VP, [_VP]),
+    ("fb_comm_buffer_bytes", _SZ, [_VP]),
+    ("fb_comm_rank", _I32, [_VP]),
+    ("fb_comm_world", _I32, [_VP]),
+    ("fb_comm_sum_fused", _I32, [_VP, _SZ, _SZ, _SZ, _I32]),
+    ("fb_comm_sum_nccl", _I32, [_VP, _VP, _SZ, _VP, _I32]),
+    ("fb_comm_allgather", _I32, [_VP, _VP, _VP, _SZ]),
+    ("fb_comm_selftest_emulated", _I32, [_VP, _I32, _VP, _SZ, _VP, _I32, _I32]),
     ("fb_conv_wgrad_static_scratch_bytes", _SZ, []),
     ("fb_conv_wgrad_static", _I32, [_VP, _VP, _VP, _VP] + [_I32] * 15),
 ]
@@ -150,6 +164,9 @@ class Handle:
         _check(lib().fb_device_kernel_error(self._ptr, ctypes.byref(w)))
         return w.value
 
+    def clearKernelError(self) -> None:
+        _check(lib().fb_device_clear_kernel_error(self._ptr))
+
     def close(self):
         if self._ptr:
             lib().fb_device_close(self._ptr)
@@ -170,6 +187,8 @@ class Buffer:
         self._handle = handle  # keeps the device alive as long as the buffer
         # dims of the dense (physical order) array; graphs with dynamic dims read them at execute
         self.shape: Optional[List[int]] = [int(v) for v in shape] if shape is not None else None
+        self._dptr: Optional[int] = None
+        self._bytes: Optional[int] = None
 
     @staticmethod
     def allocate(handle: Handle, shape: Sequence[int], data: np.ndarray) -> "Buffer":
@@ -220,10 +239,14 @@ class Buffer:
         _check(lib().fb_buffer_d2h(handle._ptr, self._ptr, out.ctypes.data_as(_VP), out.nbytes))
 
     def ptr(self) -> int:
-        return lib().fb_buffer_ptr(self._ptr) or 0
+        if self._dptr is None:  # fixed at creation: asked once
+            self._dptr = lib().fb_buffer_ptr(self._ptr) or 0
+        return self._dptr
 
     def size(self) -> int:
-        return lib().fb_buffer_size(self._ptr)
+        if self._bytes is None:
+            self._bytes = lib().fb_buffer_size(self._ptr)
+        return self._bytes
 
     def release(self):
         if self._ptr:

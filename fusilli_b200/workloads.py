@@ -7,10 +7,40 @@ from __future__ import annotations
 
 from typing import Tuple
 
+import numpy as np
+
 from .graph import (BatchnormAttr, ConvDGradAttr, ConvFPropAttr, ConvWGradAttr, DataType, LayernormAttr, MatmulAttr,
                     NormFwdPhase, PointwiseAttr, ReductionAttr, RmsnormAttr, SdpaAttr, TensorAttr,
                     channelsLastStride, contiguousStride)
 from .runtime import Graph
+
+
+# Seeds of the benchmarked configurations: one generator per (configuration, tensor), tensors
+# numbered in declaration order, so any tensor can be regenerated alone and a rank can draw just
+# its shard's source tensor. Configurations are numbered from 0 in the order the benchmark
+# lists them (fp32 conv, batched matmul, attention, ResNet-50 layers, norms).
+SEED_BASE = 0x5EED
+
+RESNET_LAYERS = [  # (C, H = W, K, R = S, pad) of the bf16 convolution sweep at N = 256
+    (64, 56, 64, 1, 0), (64, 56, 64, 3, 1), (128, 28, 128, 3, 1), (256, 14, 1024, 1, 0), (512, 7, 512, 3, 1)]
+
+
+def seeded_values(config: int, tensor_index: int, count: int, dist) -> np.ndarray:
+    """`count` float32 values of tensor number `tensor_index` of configuration `config`;
+    dist = ("normal", mean, std) or ("uniform", lo, hi)."""
+    rng = np.random.default_rng([SEED_BASE + int(config), int(tensor_index)])
+    if dist[0] == "normal":
+        v = rng.standard_normal(count, dtype=np.float32)
+        v *= np.float32(dist[2])
+        if dist[1]:
+            v += np.float32(dist[1])
+        return v
+    if dist[0] == "uniform":
+        v = rng.random(count, dtype=np.float32)
+        v *= np.float32(dist[2] - dist[1])
+        v += np.float32(dist[1])
+        return v
+    raise ValueError(dist)
 
 
 def _new(name: str, io: DataType, inter: DataType = DataType.Float) -> Graph:
@@ -39,28 +69,33 @@ def conv_fprop_bias_relu(n, c, h, w, k, r, s, pad, dtype=DataType.Float, stride=
     return g, ins, y
 
 
-def conv_dgrad(n, c, h, w, k, r, s, pad, dtype=DataType.BFloat16, stride=1, name="conv_dgrad"):
+def conv_dgrad(n, c, h, w, k, r, s, pad, dtype=DataType.BFloat16, stride=1, name="conv_dgrad", dilation=1):
     g = _new(name, dtype, dtype)
-    p = 1 + (h + 2 * pad - (r - 1) - 1) // stride
-    q = 1 + (w + 2 * pad - (s - 1) - 1) // stride
+    p = 1 + (h + 2 * pad - (r - 1) * dilation - 1) // stride
+    q = 1 + (w + 2 * pad - (s - 1) * dilation - 1) // stride
     dy = g.tensor(TensorAttr().setName("dy").setDim([n, k, p, q]).setStride(channelsLastStride([n, k, p, q])))
     wt = g.tensor(TensorAttr().setName("w").setDim([k, c, r, s]).setStride(channelsLastStride([k, c, r, s])))
     dx = g.convDGrad(dy, wt, ConvDGradAttr().setPadding([pad, pad]).setStride([stride, stride])
-                     .setDilation([1, 1]).setName("dgrad"))
+                     .setDilation([dilation, dilation]).setName("dgrad"))
     dx.setName("dx").setDim([n, c, h, w]).setOutput(True)
     g.validate()
     return g, {"dy": dy, "w": wt}, dx
 
 
-def conv_wgrad(n, c, h, w, k, r, s, pad, dtype=DataType.BFloat16, stride=1, name="conv_wgrad"):
+def conv_wgrad(n, c, h, w, k, r, s, pad, dtype=DataType.BFloat16, stride=1, name="conv_wgrad", dw_dtype=None,
+               dilation=1):
+    """dy, x NHWC of `dtype`; dw KRSC of `dw_dtype` (default `dtype`; Float keeps the fp32 sum, which
+    is what a rank contributes to the cross-rank exchange before the one rounding)."""
     g = _new(name, dtype, dtype)
-    p = 1 + (h + 2 * pad - (r - 1) - 1) // stride
-    q = 1 + (w + 2 * pad - (s - 1) - 1) // stride
+    p = 1 + (h + 2 * pad - (r - 1) * dilation - 1) // stride
+    q = 1 + (w + 2 * pad - (s - 1) * dilation - 1) // stride
     dy = g.tensor(TensorAttr().setName("dy").setDim([n, k, p, q]).setStride(channelsLastStride([n, k, p, q])))
     x = g.tensor(TensorAttr().setName("x").setDim([n, c, h, w]).setStride(channelsLastStride([n, c, h, w])))
     dw = g.convWGrad(dy, x, ConvWGradAttr().setPadding([pad, pad]).setStride([stride, stride])
-                     .setDilation([1, 1]).setName("wgrad"))
+                     .setDilation([dilation, dilation]).setName("wgrad"))
     dw.setName("dw").setDim([k, c, r, s]).setOutput(True)
+    if dw_dtype is not None:
+        dw.setDataType(dw_dtype)
     g.validate()
     return g, {"dy": dy, "x": x}, dw
 

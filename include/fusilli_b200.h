@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define FB_ABI_VERSION 2
+#define FB_ABI_VERSION 3
 #define FB_MAX_RANK 8
 #define FB_MAX_NODE_INPUTS 6
 #define FB_MAX_NODE_OUTPUTS 3
@@ -355,6 +355,77 @@ fb_status fb_plan_workspace_size_shaped(fb_plan *plan, const int64_t *arg_dims,
  * it with a stream synchronise. */
 fb_status fb_device_kernel_error(fb_device *dev, uint32_t *error_word);
 
+/* Test hook for the bounded waits: launches a one-CTA kernel that waits, with a limit of
+ * `spins` polls, on an mbarrier nothing ever arrives at, then returns normally. The wait runs
+ * out, the kernel ORs `code` into the device's error word and ends; the context stays usable.
+ * This is how failure detection is exercised without faulting or hanging the GPU. */
+fb_status fb_device_selftest_wait_timeout(fb_device *dev, uint32_t spins, uint32_t code);
+/* Clears the device's error word (stream ordered). */
+fb_status fb_device_clear_kernel_error(fb_device *dev);
+
+/* ---- multi-GPU exchange ---------------------------------------------------
+ * No counterpart in the reference, which has no multi-device code: one Handle
+ * is one device (include/fusilli/backend/runtime.h:19-24, handle.h:74-112
+ * `create(backend, deviceId)`). The sharded benchmark runs one process per GPU,
+ * each with its own fb_device; every op shards over its outermost extent with no
+ * exchange except the convolution weight gradient (benchmarks/driver.cpp:249
+ * builds the graph that is sharded): per-rank fp32 partial filter gradients are
+ * summed across ranks and rounded once.
+ *
+ * Bootstrap (the launcher moves the bytes; any transport will do):
+ *   fb_comm_create        on every rank: allocates this rank's exchange buffer
+ *   fb_comm_local_handle  on every rank: FB_COMM_HANDLE_BYTES describing it
+ *                         (rank 0's block also carries the NCCL unique id)
+ *   -- all-gather the blocks in rank order --
+ *   fb_comm_connect       on every rank, collectively: maps the peers' buffers
+ *                         (cudaIpc) and creates the NCCL communicator
+ * All exchange calls are enqueued on the device's stream and do not synchronise
+ * the host; every rank must issue the same sequence of calls. */
+#define FB_COMM_MAX_RANKS 8
+#define FB_COMM_HANDLE_BYTES 256
+typedef struct fb_comm fb_comm;
+
+fb_status fb_comm_create(fb_device *dev, int32_t rank, int32_t world,
+                         size_t buffer_bytes /* multiple of 256 */,
+                         fb_comm **out);
+fb_status fb_comm_local_handle(fb_comm *comm,
+                               uint8_t *block /* FB_COMM_HANDLE_BYTES */);
+fb_status fb_comm_connect(fb_comm *comm,
+                          const uint8_t *blocks /* world x FB_COMM_HANDLE_BYTES */);
+fb_status fb_comm_close(fb_comm *comm);
+/* This rank's exchange buffer (device memory, 256-byte aligned): bind weight
+ * gradient outputs and read results inside it. */
+void *fb_comm_buffer(fb_comm *comm);
+size_t fb_comm_buffer_bytes(fb_comm *comm);
+int32_t fb_comm_rank(fb_comm *comm);
+int32_t fb_comm_world(fb_comm *comm);
+/* Sum over ranks of the fp32 bucket at byte offset `in_offset` of every rank's
+ * exchange buffer (`count` values, a multiple of 4), rounded once to `out_dtype`
+ * (FB_DT_FLOAT / BFLOAT16 / HALF) and written at `out_offset` of EVERY rank's
+ * buffer: one kernel per rank over peer-mapped memory (plain loads and stores
+ * over NVLink, ranks added in rank order, so all ranks hold identical bits). The
+ * input bucket may be rewritten, and the output read, by the next work on the
+ * stream. Waits are bounded: a rank that never arrives sets the device's error
+ * word instead of hanging the others. */
+fb_status fb_comm_sum_fused(fb_comm *comm, size_t in_offset, size_t count,
+                            size_t out_offset, int32_t out_dtype);
+/* The same sum through the library route: ncclAllReduce(sum, fp32) in place on
+ * `inout_f32` (any device memory), then a cast of `count` values into `out`. */
+fb_status fb_comm_sum_nccl(fb_comm *comm, void *inout_f32, size_t count,
+                           void *out, int32_t out_dtype);
+/* Gathers every rank's slab of `bytes_per_rank` into `recv` in rank order
+ * (ncclAllGather): the output all-gather of the batch-sharded ops. */
+fb_status fb_comm_allgather(fb_comm *comm, const void *send, void *recv,
+                            size_t bytes_per_rank);
+/* Test entry point: runs the fused exchange for `world` VIRTUAL ranks in one
+ * cooperative launch on one device (kernels that wait on one another are never
+ * separate launches on one GPU). `buckets`: world x count fp32 (device memory);
+ * `out`: world x count values of `out_dtype`, rank r's copy at r*count. */
+fb_status fb_comm_selftest_emulated(fb_device *dev, int32_t world,
+                                    const float *buckets, size_t count,
+                                    void *out, int32_t out_dtype,
+                                    int32_t repeats);
+
 /* ---- allocation-free weight gradient -------------------------------------
  * No counterpart in the reference: its graphs always run with whatever
  * transient memory the runtime allocates for them.
@@ -372,8 +443,11 @@ fb_status fb_device_kernel_error(fb_device *dev, uint32_t *error_word);
  * until the process exits.
  *
  *  - runs on the CURRENT device, on `stream` (a cudaStream_t, may be NULL);
- *  - the first call on each device resolves the array's device address; make
- *    that call before starting any stream capture on that device;
+ *  - the first call on each device resolves the array's device address and reads
+ *    the SM count; the CUDA runtime may load this library's device code onto
+ *    that GPU at that point, which can allocate. Make that first call (any valid
+ *    small problem will do) during set-up: outside the region where allocation
+ *    is forbidden, and before starting any stream capture on that device;
  *  - fails with FB_INVALID_ARGUMENT when k*(c/groups)*r*s fp32 values do not fit
  *    in the array -- use a plan with a caller-provided workspace for those;
  *  - all calls on a device share the one array: two calls whose kernels can

@@ -75,6 +75,7 @@ REFERENCE_SAMPLES = [
     "samples/batchnorm/batchnorm_infer_nhwc_scale_bias.cpp",
     "samples/batchnorm/batchnorm_train_nchw.cpp",
     "samples/batchnorm/batchnorm_train_nchw_scale_bias.cpp",
+    "samples/aot/single_backend.cpp",
     "samples/dynamic_shapes/conv_fprop_dynamic_batch.cpp",
     "samples/dynamic_shapes/sdpa_basic_dynamic_sequence.cpp",
 ]

@@ -12,6 +12,7 @@
 
 #include <cstdlib>
 #include <filesystem>
+#include <fstream>
 #include <string>
 
 using namespace fusilli;
@@ -153,6 +154,85 @@ TEST_CASE("plans build without a device and land in the cache directory", "[grap
   }
   // remove=true cleans up after the graph goes away
   REQUIRE(!std::filesystem::exists(dir / ".cache" / "fusilli" / "cache_me" / FUSILLI_B200_OUTPUT_FILENAME));
+  std::filesystem::remove_all(dir);
+  unsetenv("FUSILLI_CACHE_DIR");
+}
+
+TEST_CASE("in-process compile cache: hit only for the same instance, name, plan input and command", "[graph][cache]") {
+  // The rules of the reference's Graph::validateCache (include/fusilli/graph/graph.h:557-644). A hit is
+  // made visible by tampering with the cached output file: a hit returns the tampered bytes, a miss a
+  // freshly built plan.
+  const auto dir = std::filesystem::temp_directory_path() / "fusilli_b200_host_test_cache_rules";
+  std::filesystem::remove_all(dir);
+  setenv("FUSILLI_CACHE_DIR", dir.c_str(), 1);
+  auto build = [](Graph &g, const std::string &name, int64_t cols) {
+    g.setName(name).setIODataType(DataType::Float).setComputeDataType(DataType::Float);
+    auto a = g.tensor(TensorAttr().setName("a").setDim({4, cols}).setStride({cols, 1}));
+    auto b = g.tensor(TensorAttr().setName("b").setDim({4, cols}).setStride({cols, 1}));
+    PointwiseAttr add;
+    add.setName("add").setMode(PointwiseAttr::Mode::ADD);
+    auto y = g.pointwise(a, b, add);
+    y->setName("y").setOutput(true);
+    return y;
+  };
+  auto tamper = [&](const std::string &sub) {
+    std::ofstream f(dir / ".cache" / "fusilli" / sub / FUSILLI_B200_OUTPUT_FILENAME, std::ios::binary | std::ios::trunc);
+    f << "TAMPERED";
+  };
+  auto isTampered = [](const std::vector<uint8_t> &v) { return std::string(v.begin(), v.end()) == "TAMPERED"; };
+  {
+    Graph g;
+    build(g, "rules_one", 8);
+    FUSILLI_REQUIRE_OK(g.validate());
+    // 1. nothing cached for this instance yet: miss, a real plan
+    FUSILLI_REQUIRE_ASSIGN(auto first, g.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(fb_plan_check(first.data(), first.size()) == FB_OK);
+    // 2. same instance, same name, same plan input, same command: hit (the file's bytes come back)
+    tamper("rules_one");
+    FUSILLI_REQUIRE_ASSIGN(auto second, g.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(isTampered(second));
+    // 3. the name (and therefore every cache path) changed: miss, built again under the new name
+    g.setName("rules_two");
+    FUSILLI_REQUIRE_ASSIGN(auto third, g.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(fb_plan_check(third.data(), third.size()) == FB_OK);
+    REQUIRE(std::filesystem::exists(dir / ".cache" / "fusilli" / "rules_two" / FUSILLI_B200_OUTPUT_FILENAME));
+    // 4. the command on file differs from the one this build would run: miss
+    tamper("rules_two");
+    {
+      std::ofstream f(dir / ".cache" / "fusilli" / "rules_two" / FUSILLI_B200_COMMAND_FILENAME, std::ios::trunc);
+      f << "some other compiler --flags\n";
+    }
+    FUSILLI_REQUIRE_ASSIGN(auto fourth, g.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(!isTampered(fourth));
+    // 5. the plan input on file differs from the one generated now: miss
+    tamper("rules_two");
+    {
+      std::ofstream f(dir / ".cache" / "fusilli" / "rules_two" / FUSILLI_B200_INPUT_FILENAME, std::ios::app);
+      f << "tensor extra\n";
+    }
+    FUSILLI_REQUIRE_ASSIGN(auto fifth, g.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(!isTampered(fifth));
+    REQUIRE(fifth == third);
+  }
+  {
+    // 6. another instance with the same name and the same graph does not inherit the cache
+    tamper("rules_two");
+    Graph other;
+    build(other, "rules_two", 8);
+    FUSILLI_REQUIRE_OK(other.validate());
+    FUSILLI_REQUIRE_ASSIGN(auto fresh, other.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(!isTampered(fresh));
+    // 7. same instance and name, different graph contents (the generated plan input differs): miss
+    Graph wider;
+    build(wider, "rules_three", 8);
+    FUSILLI_REQUIRE_OK(wider.validate());
+    FUSILLI_REQUIRE_ASSIGN(auto w1, wider.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    Graph wider2;
+    build(wider2, "rules_three", 16);
+    FUSILLI_REQUIRE_OK(wider2.validate());
+    FUSILLI_REQUIRE_ASSIGN(auto w2, wider2.compileToArtifact(Backend::CUDA, /*remove=*/false));
+    REQUIRE(w1 != w2);
+  }
   std::filesystem::remove_all(dir);
   unsetenv("FUSILLI_CACHE_DIR");
 }

@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} declared in fusilli_b200.h but not exported"
     bound = {n for n, _, _ in runtime.ABI_SYMBOLS}
     assert declared == bound, (declared - bound, bound - declared)
-    assert runtime.lib().fb_abi_version() == 2
+    assert runtime.lib().fb_abi_version() == 3
 
 
 def test_status_codes_match_error_codes():
@@ -252,17 +252,17 @@ def test_mixed_precision_matmul_needs_rank_3_and_equal_batch():
     assert "Mixed precision matmul is only supported when input tensors A and B are of rank 3" in e.value.message
 
 
-def test_matmul_batch_broadcast_by_a_divisor_is_refused_at_plan_build():
+def test_matmul_batch_broadcast_by_a_divisor_builds_a_plan():
     """The reference's validation lets a batch dim divide the other operand's (matmul_node.h:140-150);
-    the kernels broadcast from 1 only, and the refusal comes from the plan build, not from execute."""
+    the plan accepts it (the smaller operand is read modulo its batch extent) and the result has the
+    larger batch."""
     g = fz.Graph()
     g.setName("mm_divisor").setIODataType(DataType.Float).setComputeDataType(DataType.Float)
     g.setIntermediateDataType(DataType.Float)
     a = g.tensor(TensorAttr().setName("a").setDim([4, 8, 16]).setStride([128, 16, 1]))
     b = g.tensor(TensorAttr().setName("b").setDim([2, 16, 8]).setStride([128, 8, 1]))
-    g.matmul(a, b, fz.MatmulAttr().setName("mm")).setName("c").setOutput(True)
+    c = g.matmul(a, b, fz.MatmulAttr().setName("mm"))
+    c.setName("c").setOutput(True)
     g.validate()
-    with pytest.raises(FusilliError) as e:
-        g.compileToArtifact()
-    assert e.value.code == ErrorCode.NotImplemented
-    assert "proper divisor" in e.value.message
+    assert c.dim == [4, 8, 8]
+    assert runtime.lib().fb_plan_check(g.compileToArtifact(), len(g.compileToArtifact())) == 0

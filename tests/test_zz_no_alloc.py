@@ -3,9 +3,10 @@ allocate (allocator hooks, no-allocation real-time loops, plugins that only get 
 pointers and a stream). Its split-reduction scratch is a fixed array inside the
 library instead of a caller-provided workspace.
 
-Checked against the existing planned path (Graph.compile/execute with a workspace)
-on the same bytes, on two calls in a row so the second call runs over whatever the
-first left in the shared array. Collected last on purpose."""
+Checked against the CPU oracle AND against the existing planned path
+(Graph.compile/execute with a workspace) on the same bytes, on two calls in a row so
+the second call runs over whatever the first left in the shared array. Collected last
+on purpose."""
 import ctypes
 
 import numpy as np
@@ -13,9 +14,9 @@ import pytest
 
 import fusilli_b200 as fz
 from fusilli_b200 import runtime
-from fusilli_b200 import workloads as wl
-from fusilli_b200.graph import DataType, ErrorCode
-from helpers import compare, make_input, run_gpu
+from fusilli_b200.graph import DataType, ErrorCode, TensorAttr, channelsLastStride
+from helpers import compare, graph_traits, make_input, run_gpu
+from oracle import fusilli_oracle as orc
 
 
 def test_static_entry_point_is_exported_and_sized():
@@ -23,31 +24,50 @@ def test_static_entry_point_is_exported_and_sized():
     assert lib.fb_conv_wgrad_static_scratch_bytes() == 8 << 20
 
 
+def _wgrad_graph(dtype, n, c, h, w, k, r, s, pad, stride, groups):
+    g = fz.Graph()
+    g.setName("wgrad_static_ref").setIODataType(dtype).setComputeDataType(DataType.Float).setIntermediateDataType(dtype)
+    p = 1 + (h + 2 * pad - (r - 1) - 1) // stride
+    q = 1 + (w + 2 * pad - (s - 1) - 1) // stride
+    dy = g.tensor(TensorAttr().setName("dy").setDim([n, k, p, q]).setStride(channelsLastStride([n, k, p, q])))
+    x = g.tensor(TensorAttr().setName("x").setDim([n, c, h, w]).setStride(channelsLastStride([n, c, h, w])))
+    dw = g.convWGrad(dy, x, fz.ConvWGradAttr().setPadding([pad, pad]).setStride([stride, stride]).setDilation([1, 1]))
+    dw.setName("dw").setDim([k, c // groups, r, s]).setOutput(True)
+    g.validate()
+    return g, dy, x, dw
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,shape", [
-    (DataType.BFloat16, (8, 64, 28, 28, 64, 3, 3, 1)),   # split reduction through the static array
-    (DataType.Float, (4, 32, 14, 14, 48, 1, 1, 0)),
+    # n, c, h, w, k, r, s, pad, stride, groups
+    (DataType.BFloat16, (8, 64, 28, 28, 64, 3, 3, 1, 1, 1)),   # split reduction through the static array
+    (DataType.Float, (4, 32, 14, 14, 48, 1, 1, 0, 1, 1)),
+    (DataType.Float, (4, 16, 8, 8, 32, 1, 1, 0, 2, 4)),       # the reference's grouped, strided wgrad sample geometry
+    (DataType.Half, (6, 32, 17, 17, 48, 3, 3, 1, 2, 2)),      # grouped + stride 2 + padding, odd extent
 ])
-def test_static_wgrad_matches_planned_path_twice(dtype, shape):
-    n, c, h, w, k, r, s, pad = shape
-    g, ins, dw_t = wl.conv_wgrad(n, c, h, w, k, r, s, pad, dtype)
+def test_static_wgrad_matches_oracle_and_planned_path_twice(dtype, shape):
+    n, c, h, w, k, r, s, pad, stride, groups = shape
+    g, dy_t, x_t, dw_t = _wgrad_graph(dtype, n, c, h, w, k, r, s, pad, stride, groups)
     rng = np.random.default_rng(99)
-    data = {ins["dy"]: make_input(ins["dy"], rng, ("normal", 0.0, 0.1)),
-            ins["x"]: make_input(ins["x"], rng, ("normal", 0.0, 0.5))}
+    data = {dy_t: make_input(dy_t, rng, ("normal", 0.0, 0.1)), x_t: make_input(x_t, rng, ("normal", 0.0, 0.5))}
+    want = orc.execute(g, data)[dw_t]                 # the CPU oracle
+    acc_len, chained = graph_traits(g)
     handle = fz.Handle.create(fz.Backend.CUDA)
-    want = run_gpu(g, data, handle)[dw_t]           # existing entry point (workspace scratch)
+    planned = run_gpu(g, data, handle)[dw_t]           # existing entry point (workspace scratch)
+    compare(planned, want, dtype, "planned path vs oracle", acc_len, chained)
 
     lib = runtime.lib()
-    dy = fz.Buffer.allocate(handle, [data[ins["dy"]].size], data[ins["dy"]])
-    x = fz.Buffer.allocate(handle, [data[ins["x"]].size], data[ins["x"]])
+    dy = fz.Buffer.allocate(handle, [data[dy_t].size], data[dy_t])
+    x = fz.Buffer.allocate(handle, [data[x_t].size], data[x_t])
     np_dt = want.dtype
     for call in range(2):
         out = fz.Buffer.allocate(handle, [want.size], np.full(want.size, 0x7F7F if np_dt == np.uint16 else 3.0, np_dt))
         st = lib.fb_conv_wgrad_static(ctypes.c_void_p(handle.stream()), dy.ptr(), x.ptr(), out.ptr(), int(dtype),
-                                      n, c, h, w, k, r, s, pad, pad, 1, 1, 1, 1, 1)
+                                      n, c, h, w, k, r, s, pad, pad, stride, stride, 1, 1, groups)
         assert st == 0, lib.fb_last_error().decode()
         got = out.read(handle, np_dt)
-        compare(got, want, dtype, f"call {call}", scale_atol=0.5)
+        compare(got, want, dtype, f"static entry point vs oracle, call {call}", acc_len, chained)
+        compare(got, planned, dtype, f"static entry point vs planned path, call {call}", acc_len, chained)
 
 
 @pytest.mark.gpu

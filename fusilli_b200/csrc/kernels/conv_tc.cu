@@ -635,12 +635,12 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     FB_REQUIRE(encode_tmap_2byte(&tmB, wptr, 4, w_dims, w_str, v.dgrad ? wbox_d : wbox_f, &why),
                FB_RUNTIME_FAILURE, why);
   }
-  cudaError_t ae = cudaFuncSetAttribute(conv_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("conv_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
   int grid = std::min<int>(p.total_tiles, cx.dev->sm_count);
   if (halo) {
-    ae = cudaFuncSetAttribute(conv_halo_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_halo_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
     FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
                std::string("conv_halo_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
     conv_halo_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);

@@ -428,7 +428,7 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
     FB_REQUIRE(encode_tmap_2byte(&tmX, xp, 4, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
   }
   cudaError_t ae =
-      cudaFuncSetAttribute(conv_wgrad_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      set_max_dynamic_smem(reinterpret_cast<const void *>(conv_wgrad_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("conv_wgrad_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
   const int grid = t.k_tiles * t.c_tiles * t.ngroups * t.slices;

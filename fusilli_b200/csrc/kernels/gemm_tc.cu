@@ -17,7 +17,11 @@
 // Every mbarrier wait is bounded; on expiry the kernel records an error word and
 // drains instead of spinning.
 #include <algorithm>
+#include <array>
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "../common.h"
 #include "sm100.cuh"
@@ -261,8 +265,19 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
-                       const uint64_t *strides_bytes, const uint32_t *box, const char **why) {
+// FUSILLI_B200_NO_LAUNCH_CACHE=1 re-encodes every tensor map and sets the shared-memory attribute on
+// every launch, as the first version of this library did: the switch exists to measure what the
+// caches below save on the host.
+static bool launch_cache_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("FUSILLI_B200_NO_LAUNCH_CACHE");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+static bool encode_tmap_2byte_now(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                                  const uint64_t *strides_bytes, const uint32_t *box, const char **why) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     *why = "cuTensorMapEncodeTiled entry point not available";
@@ -284,6 +299,68 @@ bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint6
     return false;
   }
   return true;
+}
+
+// A tensor map is a pure function of (base address, dims, strides, box): a plan executed again on
+// the same buffers finds its maps here instead of going through the driver on every launch.
+namespace {
+struct TmapKey {
+  const void *base;
+  int32_t rank;
+  uint64_t dims[5], strides[4];
+  uint32_t box[5];
+  bool operator==(const TmapKey &o) const { return memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey &k) const {
+    uint64_t h = 1469598103934665603ull;
+    const unsigned char *p = reinterpret_cast<const unsigned char *>(&k);
+    for (size_t i = 0; i < sizeof(TmapKey); ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return (size_t)h;
+  }
+};
+std::mutex g_tmap_mutex;
+std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> g_tmap_cache;
+constexpr size_t kTmapCacheMax = 4096;
+} // namespace
+
+bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                       const uint64_t *strides_bytes, const uint32_t *box, const char **why) {
+  if (!launch_cache_enabled()) return encode_tmap_2byte_now(map, base, rank, dims, strides_bytes, box, why);
+  TmapKey key;
+  memset(&key, 0, sizeof(key)); // padding and unused slots compare equal
+  key.base = base;
+  key.rank = rank;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides_bytes[i];
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  auto it = g_tmap_cache.find(key);
+  if (it != g_tmap_cache.end()) {
+    *map = it->second;
+    return true;
+  }
+  if (!encode_tmap_2byte_now(map, base, rank, dims, strides_bytes, box, why)) return false;
+  if (g_tmap_cache.size() >= kTmapCacheMax) g_tmap_cache.clear();
+  g_tmap_cache.emplace(key, *map);
+  return true;
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is per function and device: set once, not per launch.
+cudaError_t set_max_dynamic_smem(const void *func, int bytes, int device) {
+  if (!launch_cache_enabled()) return cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  static std::mutex mu;
+  static std::unordered_map<const void *, std::array<int, 64>> set_bytes; // function -> bytes set per device
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = set_bytes.find(func);
+  if (it == set_bytes.end()) it = set_bytes.emplace(func, std::array<int, 64>{}).first;
+  const bool tracked = device >= 0 && device < 64;
+  if (tracked && it->second[device] >= bytes) return cudaSuccess; // already large enough
+  cudaError_t e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && tracked) it->second[device] = bytes;
+  return e;
 }
 
 } // namespace sm100
@@ -488,13 +565,10 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
       FB_REQUIRE(encode_tmap_2byte(&tmB, bptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
     }
   }
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  // per-device attribute; cheap enough to set on every launch of a new device
-  attr_err = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t attr_err =
+      set_max_dynamic_smem(reinterpret_cast<const void *>(gemm_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(attr_err == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("gemm_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
-  (void)attr_once;
   int grid = std::min<int>(p.total_work, cx.dev->sm_count);
   gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
   return FB_OK;

@@ -377,14 +377,12 @@ __global__ void __launch_bounds__(THREADS, 2) norm_rows_staged_kernel(const Norm
 template <typename T, typename P, int V, int THREADS>
 static bool launch_staged_v(const NormParams &p, int sm_count, cudaStream_t st) {
   const size_t smem = (size_t)kStagedStages * p.row * sizeof(T) + 64 + 2 * (THREADS / 32) * sizeof(float2);
-  static bool configured = false; // per instantiation
-  if (!configured) {
-    if (cudaFuncSetAttribute(norm_rows_staged_kernel<T, P, V, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return false;
-    }
-    configured = true;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      sm100::set_max_dynamic_smem(reinterpret_cast<const void *>(norm_rows_staged_kernel<T, P, V, THREADS>), (int)smem,
+                                  device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
   }
   const int blocks = (int)std::min<int64_t>(p.batch, (int64_t)sm_count * 2);
   norm_rows_staged_kernel<T, P, V, THREADS><<<blocks, THREADS, smem, st>>>(p);

@@ -462,7 +462,7 @@ fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s) {
     FB_REQUIRE(encode_tmap_2byte(&tk, kp, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
     FB_REQUIRE(encode_tmap_2byte(&tv, vp, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
   }
-  cudaError_t ae = cudaFuncSetAttribute(sdpa_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t ae = set_max_dynamic_smem(reinterpret_cast<const void *>(sdpa_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("sdpa_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
   dim3 grid((unsigned)p.q_blocks, (unsigned)(p.B * p.Hq));

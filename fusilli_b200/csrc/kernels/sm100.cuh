@@ -269,6 +269,8 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, int ab_forma
 // Returns false (message in *why) if the driver rejects the encoding.
 bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
                        const uint64_t *strides_bytes, const uint32_t *box, const char **why);
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of per launch.
+cudaError_t set_max_dynamic_smem(const void *func, int bytes, int device);
 
 } // namespace sm100
 } // namespace fb

@@ -26,7 +26,7 @@ OUT = os.path.join(HERE, "_build")
 REFERENCE = os.environ.get("FUSILLI_REFERENCE_DIR", os.path.normpath(os.path.join(ROOT, "..", "reference")))
 CXX = os.environ.get("FUSILLI_TEST_CXX", "/usr/bin/g++")
 
-OWN_SOURCES = ["test_frontend_host.cpp", "test_frontend_device.cpp"]
+OWN_SOURCES = ["test_frontend_host.cpp", "test_frontend_device.cpp", "host_execute_latency.cpp"]
 
 # Reference programs that only need the graph API of the operators in scope. Paths are relative
 # to the reference checkout. SDPA samples there go through a user-supplied MLIR custom op and

@@ -25,6 +25,7 @@ SOURCES = [
     "kernels/gemm_tc.cu",
     "kernels/conv_tc.cu",
     "kernels/conv_wgrad_tc.cu",
+    "kernels/conv_split_f32.cu",
     "kernels/sdpa_tc.cu",
     "kernels/selftest.cu",
 ]

@@ -95,6 +95,7 @@ enum StepKind : int32_t {
 enum Engine : int32_t {
   ENGINE_SIMT = 0,    // CUDA-core kernels: any dtype/stride the op allows
   ENGINE_TCGEN05 = 1, // tcgen05/TMEM/TMA kernels: 16-bit operands, aligned shapes
+  ENGINE_TCGEN05_SPLIT = 2, // fp32 forward convolution as bf16 piece products on tcgen05 (fp32-grade results)
 };
 
 constexpr int kMaxEpilogueOps = 6;
@@ -168,6 +169,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s);
 fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s);
 fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s);
 fb_status launch_batchnorm(const ExecContext &cx, const Step &s);
+fb_status launch_conv_split_f32(const ExecContext &cx, const Step &s);
 // Workspace the batch-statistics pass needs (0 in inference); *splits = slices of the reduction.
 int64_t batchnorm_scratch_bytes(const Plan &p, const Step &s, int32_t *splits);
 
@@ -176,6 +178,8 @@ bool gemm_tc_eligible(const Plan &p, const Step &s);
 bool conv_tc_eligible(const Plan &p, const Step &s);
 bool sdpa_tc_eligible(const Plan &p, const Step &s);
 bool conv_wgrad_tc_eligible(const Plan &p, const Step &s);
+bool conv_split_f32_eligible(const Plan &p, const Step &s);
+int64_t conv_split_f32_scratch_bytes(const Plan &p, const Step &s);
 int64_t conv_wgrad_tc_scratch_bytes(const Plan &p, const Step &s, int32_t *slices);
 // Kernel launches one execute of this step issues.
 int step_launches(const Plan &p, const Step &s);

@@ -239,6 +239,201 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
 }
 
+// ---- paired-CTA variant -----------------------------------------------------------------
+// The same GEMM on CTA pairs (clusters of two, tcgen05 cta_group::2): one 256 x 256 output tile per
+// pair, each CTA holding its own 128 rows of A and its own 128 of the 256 B columns. Per CTA and K
+// block that is 32 KB fetched from L2 instead of the 48 KB of the 128 x 256 single-CTA tile -- L2
+// to shared-memory traffic is what paces the single-CTA kernel -- and the ring has six stages.
+// Every CTA loads its own operands with ordinary (not multicast) TMA; completions are counted on
+// the leader's barrier, MMA completion is committed to both CTAs' barriers, the peer's epilogue
+// warps release the accumulator on the leader's barrier.
+namespace pair {
+constexpr int TM = 256, STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = (BN / 2) * BK * 2; // per CTA
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+} // namespace pair
+
+__device__ __forceinline__ WorkItem decode_work_pair(const GemmTcParams &p, int w) {
+  int tile = w, n_off = 0, nb = BN;
+  if (w >= p.full_tiles) {
+    const int r = w - p.full_tiles;
+    tile = p.full_tiles + (r >> 1);
+    n_off = (r & 1) * (BN / 2);
+    nb = BN / 2;
+  }
+  WorkItem it;
+  it.m0 = (tile % p.tiles_m) * pair::TM;
+  it.n0 = ((tile / p.tiles_m) % p.tiles_n) * BN + n_off;
+  it.b = tile / (p.tiles_m * p.tiles_n);
+  it.nb = nb;
+  return it;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmTcParams p) {
+  using namespace pair;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // the same offset in both CTAs
+  const uint32_t bar_base = smem_base + pair::STAGES * pair::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (pair::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * pair::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * pair::STAGES + 2 + a); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * pair::STAGES + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank(); // 0 = leader
+  const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < pair::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);  // leader's: one expect_tx arrival, bytes of both CTAs
+      mbar_init(empty_bar(s), 1); // each CTA's own: committed to by the leader's MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8); // leader's: four epilogue warps of each CTA
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS); // one warp of each CTA of the pair, collectively
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (warp == 0 || warp == 6) {
+    const uint32_t pid = warp == 0 ? 0u : 1u;
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = cluster_id; w < p.total_work && ok; w += nclusters) {
+        const WorkItem wi = decode_work_pair(p, w);
+        const int m0 = wi.m0 + (int)rank * BM, nh = wi.nb / 2, n0 = wi.n0 + (int)rank * nh;
+        const int ba = wi.b % p.a_batches, bb = wi.b % p.b_batches;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((it % PRODUCERS) != pid) continue;
+          const int s = it % pair::STAGES;
+          const uint32_t ph = (it / pair::STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2u * (uint32_t)(pair::A_BYTES + nh * BK * 2));
+          const uint32_t sa = smem_base + s * pair::STAGE_BYTES, sb = sa + pair::A_BYTES;
+          const int k0 = kb * BK;
+          if (!p.a_mn_major) {
+            tma_load_3d_pair(sa, &tmap_a, lead_full, k0, m0, ba);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_3d_pair(sa + i * (64 * BK * 2), &tmap_a, lead_full, m0 + 64 * i, k0, ba);
+          }
+          // this CTA's half of the B columns, in boxes of 64
+#pragma unroll
+          for (int i = 0; i < BN / 128; ++i)
+            if (i * 64 < nh) {
+              if (!p.b_mn_major) tma_load_3d_pair(sb + i * (64 * BK * 2), &tmap_b, lead_full, k0, n0 + 64 * i, bb);
+              else tma_load_3d_pair(sb + i * (64 * BK * 2), &tmap_b, lead_full, n0 + 64 * i, k0, bb);
+            }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0) {
+      const bool leader = elect_one();
+      const uint32_t idesc_full = make_idesc_f16(pair::TM, BN, p.ab_format, p.a_mn_major, p.b_mn_major);
+      const uint32_t idesc_half = make_idesc_f16(pair::TM, BN / 2, p.ab_format, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? 64 * BK * 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn_major ? 64 * BK * 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
+      const uint64_t a_desc0 = make_smem_desc(smem_base, a_lbo, 1024);
+      const uint64_t b_desc0 = make_smem_desc(smem_base + pair::A_BYTES, b_lbo, 1024);
+      uint32_t it = 0, lt = 0;
+      bool ok = true;
+      for (int w = cluster_id; w < p.total_work && ok; w += nclusters, ++lt) {
+        const uint32_t idesc = w < p.full_tiles ? idesc_full : idesc_half;
+        const int acc = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        if (!mbar_wait(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % pair::STAGES;
+          const uint32_t ph = (it / pair::STAGES) & 1;
+          if (!mbar_wait(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t soff = (uint64_t)((s * pair::STAGE_BYTES) >> 4);
+          if (leader) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              tc_mma_f16_pair(d_tmem, a_desc0 + soff + (uint64_t)((k * a_kstep) >> 4),
+                              b_desc0 + soff + (uint64_t)((k * b_kstep) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            // the stage is free in BOTH CTAs once these MMAs have read it
+            tc_commit_pair(map_to_cta(empty_bar(s), 0));
+            tc_commit_pair(map_to_cta(empty_bar(s), 1));
+          }
+        }
+        if (ok && leader) { // accumulator complete, in both CTAs' TMEM
+          tc_commit_pair(map_to_cta(tfull_bar(acc), 0));
+          tc_commit_pair(map_to_cta(tfull_bar(acc), 1));
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    uint32_t lt = 0;
+    bool ok = true;
+    for (int w = cluster_id; w < p.total_work && ok; w += nclusters, ++lt) {
+      const WorkItem wi = decode_work_pair(p, w);
+      const int b = wi.b, chunks = wi.nb / 32;
+      const int acc = lt & 1;
+      const uint32_t aph = (lt >> 1) & 1;
+      if (!mbar_wait(tfull_bar(acc), aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int m = wi.m0 + (int)rank * BM + q * 32 + lane;
+      const int n0 = wi.n0;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      const int64_t row_off = (int64_t)b * p.c_bstride + (int64_t)m * p.ldc;
+      const uint32_t lead_tempty = map_to_cta(tempty_bar(acc), 0);
+#pragma unroll 1
+      for (int c = 0; c < chunks; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        if (c == chunks - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(lead_tempty);
+        }
+        const int nc = n0 + c * 32;
+        if (m < p.M && nc < p.N) {
+          const int valid = min(32, p.N - nc);
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          epi_run32(p.epi, v, row_off, nc, valid);
+          epi_store32(p.out, p.epi.out_dtype, row_off + nc, v, valid);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // neither CTA leaves while the other may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 } // namespace
 
 // ---- host ------------------------------------------------------------------------
@@ -480,6 +675,44 @@ bool gemm_tc_eligible(const Plan &p, const Step &s) {
   return true;
 }
 
+// Whether clusters of two CTAs of the pair kernel can be resident on this device (asked once per
+// device), and whether the caller left the pair kernel enabled.
+static bool pair_kernel_usable(int device) {
+  static const bool enabled = [] {
+    const char *e = getenv("FUSILLI_B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled || device < 0 || device >= 64) return false;
+  static std::mutex mu;
+  static int8_t state[64] = {0}; // 0 unknown, 1 usable, -1 not
+  std::lock_guard<std::mutex> lock(mu);
+  if (state[device] == 0) {
+    state[device] = -1;
+    if (sm100::set_max_dynamic_smem(reinterpret_cast<const void *>(gemm_pair_tcgen05_kernel), pair::SMEM_BYTES,
+                                    device) == cudaSuccess) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = pair::SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void *>(gemm_pair_tcgen05_kernel), &cfg) ==
+              cudaSuccess &&
+          n >= 1)
+        state[device] = 1;
+    }
+    (void)cudaGetLastError();
+  }
+  return state[device] == 1;
+}
+
 fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   const Plan &plan = *cx.plan;
   const fb_node_desc &d = plan.nodes[s.node].d;
@@ -500,14 +733,18 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   p.a_batches = (int)g.a_nb;
   p.b_batches = (int)g.b_nb;
   p.ab_format = a.dtype == FB_DT_BFLOAT16 ? 1 : 0;
-  p.tiles_m = (p.M + BM - 1) / BM;
+  // CTA pairs (256 x 256 tiles) when the problem has at least one full pair tile of rows and the
+  // device can run clusters of two; FUSILLI_B200_GEMM_PAIR=0 keeps the single-CTA kernel.
+  const bool use_pair = g.M >= pair::TM && g.N >= BN / 2 && pair_kernel_usable(cx.dev->ordinal);
+  const int tile_m = use_pair ? pair::TM : BM;
+  p.tiles_m = (p.M + tile_m - 1) / tile_m;
   p.tiles_n = (p.N + BN - 1) / BN;
   int64_t total = (int64_t)p.tiles_m * p.tiles_n * p.batches;
   FB_REQUIRE(total < (1ll << 31), FB_NOT_IMPLEMENTED, "gemm_tcgen05: too many tiles");
   p.total_tiles = (int)total;
   {
-    // A last wave that fills at most half of the SMs runs as half tiles on twice as many SMs.
-    const int sms = cx.dev->sm_count;
+    // A last wave that fills at most half of the SMs (or SM pairs) runs as half tiles on twice as many.
+    const int sms = use_pair ? cx.dev->sm_count / 2 : cx.dev->sm_count;
     const int tail = p.total_tiles % sms;
     const bool split = tail > 0 && 2 * tail <= sms && p.N > BN / 2;
     p.full_tiles = split ? p.total_tiles - tail : p.total_tiles;
@@ -557,13 +794,22 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
     }
     if (!g.b_mn) {
       uint64_t dims[3] = {(uint64_t)g.K, (uint64_t)g.N, bb}, str[2] = {(uint64_t)g.b_ld * 2, b_bstride};
-      uint32_t box[3] = {BK, BN / 2, 1};
+      uint32_t box[3] = {BK, use_pair ? 64u : (uint32_t)(BN / 2), 1}; // the pair kernel loads 64-row boxes
       FB_REQUIRE(encode_tmap_2byte(&tmB, bptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
     } else {
       uint64_t dims[3] = {(uint64_t)g.N, (uint64_t)g.K, bb}, str[2] = {(uint64_t)g.b_ld * 2, b_bstride};
       uint32_t box[3] = {64, BK, 1};
       FB_REQUIRE(encode_tmap_2byte(&tmB, bptr, 3, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
     }
+  }
+  if (use_pair) {
+    cudaError_t pe = set_max_dynamic_smem(reinterpret_cast<const void *>(gemm_pair_tcgen05_kernel), pair::SMEM_BYTES,
+                                          cx.dev->ordinal);
+    FB_REQUIRE(pe == cudaSuccess, FB_RUNTIME_FAILURE,
+               std::string("gemm_pair_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(pe));
+    const int clusters = std::min<int>(p.total_work, cx.dev->sm_count / 2);
+    gemm_pair_tcgen05_kernel<<<2 * clusters, NUM_THREADS, pair::SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+    return FB_OK;
   }
   cudaError_t attr_err =
       set_max_dynamic_smem(reinterpret_cast<const void *>(gemm_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);

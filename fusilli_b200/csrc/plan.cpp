@@ -286,7 +286,12 @@ fb_status lower(Plan &p) {
       else if (d.op == FB_OP_CONV_WGRAD)
         s.engine = conv_wgrad_tc_eligible(p, s) ? ENGINE_TCGEN05 : ENGINE_SIMT;
       else
-        s.engine = conv_tc_eligible(p, s) ? ENGINE_TCGEN05 : ENGINE_SIMT;
+        s.engine = conv_tc_eligible(p, s) ? ENGINE_TCGEN05
+                                          : (conv_split_f32_eligible(p, s) ? ENGINE_TCGEN05_SPLIT : ENGINE_SIMT);
+      if (s.engine == ENGINE_TCGEN05_SPLIT) {
+        s.split_k = 1;
+        s.scratch_bytes = conv_split_f32_scratch_bytes(p, s);
+      }
       if (s.engine == ENGINE_TCGEN05) {
         s.split_k = 1;
         s.scratch_bytes = 0;
@@ -676,7 +681,9 @@ const char *step_kernel_name(const Plan &p, const Step &s) {
   case STEP_CONTRACT:
     switch (op) {
     case FB_OP_MATMUL: return tc ? "gemm_tcgen05" : "gemm_simt";
-    case FB_OP_CONV_FPROP: return tc ? "conv_fprop_tcgen05" : "conv_fprop_simt";
+    case FB_OP_CONV_FPROP:
+      if (s.engine == ENGINE_TCGEN05_SPLIT) return "conv_fprop_split_f32_tcgen05";
+      return tc ? "conv_fprop_tcgen05" : "conv_fprop_simt";
     case FB_OP_CONV_DGRAD: return tc ? "conv_dgrad_tcgen05" : "conv_dgrad_simt";
     case FB_OP_CONV_WGRAD: return tc ? "conv_wgrad_tcgen05" : "conv_wgrad_simt";
     }
@@ -688,6 +695,7 @@ int step_launches(const Plan &p, const Step &s) {
   if (s.kind == STEP_BATCHNORM) return (p.nodes[s.node].d.flags & FB_FLAG_NORM_TRAINING) ? 3 : 1;
   const bool wgrad = p.nodes[s.node].d.op == FB_OP_CONV_WGRAD;
   if (wgrad && s.engine == ENGINE_TCGEN05) return 2; // partial kernel + slice reduction
+  if (s.engine == ENGINE_TCGEN05_SPLIT) return 3;    // piece split of X, of W, convolution
   return s.split_k > 1 ? 2 : 1;
 }
 

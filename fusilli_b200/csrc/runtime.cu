@@ -503,7 +503,9 @@ static fb_status execute_plan(const fb_plan *plan, const Plan &p, fb_device *dev
     case STEP_NORM: st = launch_norm(cx, s); break;
     case STEP_BATCHNORM: st = launch_batchnorm(cx, s); break;
     case STEP_CONTRACT:
-      if (s.engine == ENGINE_TCGEN05) {
+      if (s.engine == ENGINE_TCGEN05_SPLIT) {
+        st = launch_conv_split_f32(cx, s);
+      } else if (s.engine == ENGINE_TCGEN05) {
         const int op = p.nodes[s.node].d.op;
         st = op == FB_OP_MATMUL ? launch_gemm_tc(cx, s)
                                 : (op == FB_OP_CONV_WGRAD ? launch_conv_wgrad_tc(cx, s) : launch_conv_tc(cx, s));

@@ -68,7 +68,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         obj = os.path.join(OBJ, src.replace("/", "_") + ".o")
         objs.append(obj)
         if force or _stale(obj, [path] + hdrs):
-            cmd = [nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
+            extra = os.environ.get("FUSILLI_B200_NVCC_EXTRA", "").split()  # e.g. -DNAME for an instrumented build
+            cmd = [nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", path, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):

@@ -5,16 +5,20 @@
 // pieces (x = x0 + x1 + x2, 8 significant bits each) multiplies exactly piece by piece. Of the nine
 // piece products of x * w the three below 2^-24 of the result are dropped; the other six are six
 // "channel blocks" of one implicit GEMM whose contraction axis is (tap, piece pair, channel):
-//   a pre-pass writes X' = [x0 | x1 | x2] and W' = [w0 | w1 | w2] in bf16 (3C channels each),
-//   K block (tap, pair (a, b), channel block) multiplies X' piece a with W' piece b.
+//   a pre-pass writes X' = [x0 | x1 | x2] and W' = [w0 | w1 | w2] in bf16 (3C channels each);
+//   a ring stage holds, for one (tap, 64-channel block), the three X' piece tiles and the three W'
+//   piece tiles, and the MMA warp multiplies the six pairs out of that one stage (each X' tile is
+//   fetched once for up to three products).
 // What is NOT exact on the tensor pipe is the running fp32 accumulation: every MMA adds its 16
 // products into the accumulator with less than a correctly rounded fp32 add, and the error grows
 // with the length of the chain and the size of the running sum. The accumulation in TMEM is
-// therefore kept SHORT: after `chunk_kb` K blocks the MMA warp publishes the accumulator and
-// starts the next chunk from zero in another TMEM buffer; the epilogue warps add the chunks into
-// fp32 registers (correctly rounded adds) and run the fused pointwise chain after the last one.
-// Within a chunk the small piece products come first and x0*w0 last, so the long part of the
-// chain runs while the accumulator is still small.
+// therefore kept SHORT: after the 24 MMAs of one stage (or of `chunk_steps` stages) the MMA warp
+// publishes the accumulator and starts the next chunk from zero in another TMEM buffer; the
+// epilogue warps add the chunks into fp32 registers (correctly rounded adds) and run the fused
+// pointwise chain after the last one. Within a stage the small piece products come first and
+// x0*w0 last, so most of the chain runs while the accumulator is still small. Measured on the
+// benchmarked 3x3 C64 layer against a float64 oracle: worst error 7.6e-6 with one tap per chain,
+// 1.8e-4 with the whole 216-MMA reduction in one chain, 4.2e-5 for a plain fp32 FMA kernel.
 //
 // Structure otherwise as the 16-bit per-tap kernel: one 4-D TMA box per (tap, K block) with zero
 // fill as padding, two producer warps, one MMA warp, eight epilogue warps, bounded waits.
@@ -34,8 +38,8 @@ namespace {
 
 constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int MAX_STAGES = 9, MAX_ACC = 8;
-constexpr int RING_BYTES = 221184; // 9 x 24 KB (BN = 64) or 6 x 32 KB (BN = 128) fit
+constexpr int MAX_STAGES = 3, MAX_ACC = 8;
+constexpr int RING_BYTES = 221184; // 3 x 72 KB (BN = 64) or 2 x 96 KB (BN = 128) fit
 constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
 constexpr int NUM_THREADS = 352; // TMA warp, MMA warp, 8 epilogue warps, second TMA warp
 constexpr int TMEM_COLS = 512;
@@ -49,7 +53,7 @@ struct SplitParams {
   int32_t bw, bh, bn, rows;
   int32_t tiles_w, tiles_h, tiles_nb, tiles_nout, total_tiles;
   int32_t BN, cb_per;   // output-channel tile, 64-channel blocks per piece
-  int32_t kblocks, chunk_kb, nchunks, nacc;
+  int32_t steps, chunk_steps, nchunks, nacc; // steps = taps x channel blocks, each one ring stage
   uint32_t a_bytes, b_bytes;
   int32_t stages, stage_bytes;
   void *out;
@@ -58,25 +62,27 @@ struct SplitParams {
   TcEpilogue epi;
 };
 
-// piece of X and piece of W multiplied by the K blocks of one tap, smallest products first
-__constant__ int kPieceA[PAIRS] = {0, 2, 1, 0, 1, 0};
-__constant__ int kPieceB[PAIRS] = {2, 0, 1, 1, 0, 0};
-
-// rows x C fp32 -> rows x 3C bf16: piece p of channel c at [row][p*C + c].
+// rows x C fp32 -> rows x 3C bf16: piece p of channel c at [row][p*C + c]. One launch splits both
+// operands: the rows of X first, then the rows of W.
 __global__ void __launch_bounds__(256)
-split3_bf16_kernel(const float *__restrict__ in, __nv_bfloat16 *__restrict__ out, int64_t rows, int C) {
+split3_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ xs, int64_t x_rows,
+                   const float *__restrict__ w, __nv_bfloat16 *__restrict__ ws, int64_t w_rows, int C) {
   const int64_t vec_per_row = C / 4;
-  const int64_t total = rows * vec_per_row;
+  const int64_t x_total = x_rows * vec_per_row, total = x_total + w_rows * vec_per_row;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / vec_per_row;
-    const int c = (int)(i - row * vec_per_row) * 4;
+    const bool is_x = i < x_total;
+    const int64_t li = is_x ? i : i - x_total;
+    const float *in = is_x ? x : w;
+    __nv_bfloat16 *out = is_x ? xs : ws;
+    const int64_t row = li / vec_per_row;
+    const int c = (int)(li - row * vec_per_row) * 4;
     const float4 v = __ldg(reinterpret_cast<const float4 *>(in + row * C + c));
-    const float x[4] = {v.x, v.y, v.z, v.w};
+    const float f[4] = {v.x, v.y, v.z, v.w};
     __nv_bfloat16 p0[4], p1[4], p2[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      p0[j] = __float2bfloat16_rn(x[j]);
-      const float r1 = x[j] - __bfloat162float(p0[j]); // exact: the difference fits in fp32
+      p0[j] = __float2bfloat16_rn(f[j]);
+      const float r1 = f[j] - __bfloat162float(p0[j]); // exact: the difference fits in fp32
       p1[j] = __float2bfloat16_rn(r1);
       const float r2 = r1 - __bfloat162float(p1[j]);
       p2[j] = __float2bfloat16_rn(r2);
@@ -139,24 +145,24 @@ conv_split_f32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       const int tp = tile % tiles_pix, tno = tile / tiles_pix;
       const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
       const int w0 = tw * p.bw + p.off_w, h0 = th * p.bh + p.off_h, n0 = tb * p.bn, no0 = tno * p.BN;
-      int cbi = 0, pr = 0, ts = 0, tr = 0; // channel block (fastest), piece pair, filter column, filter row
-      for (int kb = 0; kb < p.kblocks; ++kb, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+      int cbi = 0, ts = 0, tr = 0; // channel block (fastest), filter column, filter row
+      for (int st = 0; st < p.steps; ++st, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
         if ((it & 1u) == pid) {
           if (!mbar_wait_warp(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-          const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + A_BYTES;
-          const int ca = kPieceA[pr] * p.C + cbi * BK, cb = kPieceB[pr] * p.C + cbi * BK;
-          mbar_expect_tx_elect(full_bar(s), p.a_bytes + p.b_bytes);
-          tma_load_4d_elect(sa, &tmap_a, full_bar(s), ca, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
-          tma_load_4d_elect(sb, &tmap_b, full_bar(s), cb, ts, tr, no0);
+          const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + 3 * A_BYTES;
+          mbar_expect_tx_elect(full_bar(s), 3 * (p.a_bytes + p.b_bytes));
+#pragma unroll
+          for (int pc = 0; pc < 3; ++pc) {
+            const int c0 = pc * p.C + cbi * BK;
+            tma_load_4d_elect(sa + pc * A_BYTES, &tmap_a, full_bar(s), c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
+            tma_load_4d_elect(sb + pc * p.b_bytes, &tmap_b, full_bar(s), c0, ts, tr, no0);
+          }
         }
         if (++cbi == p.cb_per) {
           cbi = 0;
-          if (++pr == PAIRS) {
-            pr = 0;
-            if (++ts == p.S) {
-              ts = 0;
-              ++tr;
-            }
+          if (++ts == p.S) {
+            ts = 0;
+            ++tr;
           }
         }
       }
@@ -164,7 +170,7 @@ conv_split_f32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   } else if (warp == 1) {
     const uint32_t idesc = make_idesc_f16(BM, p.BN, /*bf16*/ 1, 0, 0);
     const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
-    const uint64_t b_desc0 = make_smem_desc(smem_base + A_BYTES, 16, 1024);
+    const uint64_t b_desc0 = make_smem_desc(smem_base + 3 * A_BYTES, 16, 1024);
     uint32_t ph = 0;
     int s = 0, acc = 0; // accumulator ring position and its phase
     uint32_t aph = 0;
@@ -174,14 +180,22 @@ conv_split_f32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
-        for (int j = 0; j < p.chunk_kb; ++j, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+        for (int j = 0; j < p.chunk_steps; ++j, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
           if (!mbar_wait_warp(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint64_t soff = (uint64_t)(((uint32_t)s * STAGE_BYTES) >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            tc_mma_f16_elect(d_tmem, a_desc0 + soff + (uint64_t)((k * 32) >> 4), b_desc0 + soff + (uint64_t)((k * 32) >> 4),
-                             idesc, (j > 0 || k > 0) ? 1u : 0u);
+          for (int pr = 0; pr < PAIRS; ++pr) {
+            // X piece / W piece of product `pr`, smallest products first: (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
+            const int pa = pr == 1 ? 2 : ((pr == 2 || pr == 4) ? 1 : 0);
+            const int pb = pr == 0 ? 2 : ((pr == 2 || pr == 3) ? 1 : 0);
+            const uint64_t ad = a_desc0 + soff + (uint64_t)((uint32_t)(pa * A_BYTES) >> 4);
+            const uint64_t bd = b_desc0 + soff + (uint64_t)(((uint32_t)pb * p.b_bytes) >> 4);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              tc_mma_f16_elect(d_tmem, ad + (uint64_t)((k * 32) >> 4), bd + (uint64_t)((k * 32) >> 4), idesc,
+                               (j > 0 || pr > 0 || k > 0) ? 1u : 0u);
+          }
           tc_commit_elect(empty_bar(s));
         }
         if (ok) tc_commit_elect(tfull_bar(acc));
@@ -358,11 +372,9 @@ fb_status launch_conv_split_f32(const ExecContext &cx, const Step &s) {
   __nv_bfloat16 *xs = reinterpret_cast<__nv_bfloat16 *>(cx.workspace + s.scratch_offset);
   __nv_bfloat16 *ws = reinterpret_cast<__nv_bfloat16 *>(cx.workspace + s.scratch_offset + align256(x_rows * 3 * v.C * 2));
   {
-    const int64_t xv = x_rows * (v.C / 4), wv = w_rows * (v.C / 4);
-    const int xb = (int)std::min<int64_t>((xv + 255) / 256, (int64_t)cx.dev->sm_count * 16);
-    const int wb = (int)std::min<int64_t>((wv + 255) / 256, (int64_t)cx.dev->sm_count * 16);
-    split3_bf16_kernel<<<xb, 256, 0, cx.dev->stream>>>(xptr, xs, x_rows, v.C);
-    split3_bf16_kernel<<<wb, 256, 0, cx.dev->stream>>>(wptr, ws, w_rows, v.C);
+    const int64_t vecs = (x_rows + w_rows) * (v.C / 4);
+    const int blocks = (int)std::min<int64_t>((vecs + 255) / 256, (int64_t)cx.dev->sm_count * 16);
+    split3_bf16_kernel<<<blocks, 256, 0, cx.dev->stream>>>(xptr, xs, x_rows, wptr, ws, w_rows, v.C);
   }
 
   static thread_local SplitParams p;
@@ -381,19 +393,20 @@ fb_status launch_conv_split_f32(const ExecContext &cx, const Step &s) {
   const int64_t total = (int64_t)p.tiles_w * p.tiles_h * p.tiles_nb * p.tiles_nout;
   FB_REQUIRE(total < (1ll << 31), FB_NOT_IMPLEMENTED, "conv_split_f32: too many tiles");
   p.total_tiles = (int)total;
-  p.kblocks = v.R * v.S * PAIRS * p.cb_per;
-  // Length of one accumulation in TMEM, in K blocks of 64 products per output: the piece pairs of
-  // one tap by default. FUSILLI_B200_F32_CHUNK = pair | tap | tile overrides it (for measurements).
-  p.chunk_kb = PAIRS * p.cb_per;
+  p.steps = v.R * v.S * p.cb_per;
+  // Length of one accumulation in TMEM, in ring stages of 24 MMAs (six piece products of one tap
+  // and 64-channel block): one stage by default. FUSILLI_B200_F32_CHUNK = tap | tile lengthens it
+  // (for measurements of the error against the chain length).
+  p.chunk_steps = 1;
   if (const char *e = getenv("FUSILLI_B200_F32_CHUNK")) {
-    if (strcmp(e, "pair") == 0) p.chunk_kb = p.cb_per;
-    else if (strcmp(e, "tile") == 0) p.chunk_kb = p.kblocks;
+    if (strcmp(e, "tap") == 0) p.chunk_steps = p.cb_per;
+    else if (strcmp(e, "tile") == 0) p.chunk_steps = p.steps;
   }
-  p.nchunks = p.kblocks / p.chunk_kb;
+  p.nchunks = p.steps / p.chunk_steps;
   p.nacc = std::min(MAX_ACC, TMEM_COLS / p.BN);
   p.a_bytes = (uint32_t)p.rows * BK * 2;
   p.b_bytes = (uint32_t)p.BN * BK * 2;
-  p.stage_bytes = A_BYTES + p.BN * BK * 2;
+  p.stage_bytes = 3 * (A_BYTES + p.BN * BK * 2);
   p.stages = std::min(MAX_STAGES, RING_BYTES / p.stage_bytes);
   p.out = optr;
   p.out_sn = out.strides[0]; p.out_sh = out.strides[2]; p.out_sw = out.strides[3];

@@ -33,9 +33,23 @@ constexpr int A_BYTES = BM * BK * 2;
 // layers is bytes in flight per SM against L2 latency, not bandwidth.
 constexpr int MAX_STAGES = 12;
 constexpr int RING_BYTES = 229376; // 9 x 24 KB, 7 x 32 KB or 4 x 48 KB fit
+// With 16-bit outputs the last 32 KB of that space are the epilogue's staging tiles (two boxes of
+// 128 rows x 64 channels, 128-byte swizzled) and the operand ring gets the 192 KB before them.
+constexpr int STAGING_BYTES = 32768, BOX_BYTES = 16384;
+constexpr int RING_BYTES_STAGED = RING_BYTES - STAGING_BYTES; // 8 x 24 KB, 6 x 32 KB or 4 x 48 KB
 constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
 constexpr int NUM_THREADS = 320; // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
 constexpr int TMEM_COLS = 512;
+
+#ifdef FB_CONV_TRACE
+// Instrumented build only: cycles block 0 spends in each phase (index meanings in fb_debug_conv_trace's caller).
+__device__ unsigned long long g_conv_trace[32];
+#define TR_BEGIN long long _tr0 = clock64()
+#define TR_ADD(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) { long long _t = clock64(); atomicAdd(&g_conv_trace[i], (unsigned long long)(_t - _tr0)); _tr0 = _t; } } while (0)
+#else
+#define TR_BEGIN
+#define TR_ADD(i)
+#endif
 
 struct ConvTcParams {
   int32_t dgrad;        // 0 fprop, 1 dgrad
@@ -59,6 +73,7 @@ struct ConvTcParams {
   int32_t b_stages;                      // filter ring depth when it is streamed
   void *out;
   int64_t out_sn, out_sh, out_sw;        // element strides of the output (channel stride 1)
+  int32_t tma_store;                     // 16-bit output: stage tiles in shared memory, store them by TMA
   uint32_t *err;
   TcEpilogue epi;
 };
@@ -68,7 +83,8 @@ struct ConvTcParams {
 // quarter (warp index mod 4) and split the tile's columns in halves: on layers with few channel
 // blocks per tile the epilogue, not the MMAs, sets the pace. tfull0 / tempty0 are the barriers of
 // accumulator 0; accumulator 1's follow 8 bytes later.
-__device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint32_t tmem_base, uint32_t tfull0,
+__device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const CUtensorMap *tmap_c,
+                                                    uint32_t staging, uint32_t tmem_base, uint32_t tfull0,
                                                     uint32_t tempty0, int warp, int lane) {
   const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
   const int q = warp & 3;
@@ -79,7 +95,9 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint3
     const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
     const int acc = lt & 1;
     const uint32_t aph = (lt >> 1) & 1;
+    TR_BEGIN;
     if (!mbar_wait(tfull0 + 8u * acc, aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+    if (warp == 2) TR_ADD(5); // epilogue: waiting for a finished accumulator
     tc_fence_after();
     const int row = q * 32 + lane;
     const int dw = row % p.bw, dh = (row / p.bw) % p.bh, dn = row / (p.bw * p.bh);
@@ -89,7 +107,101 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint3
     const int no0 = tno * p.BN;
     const uint32_t taddr = tmem_base + acc * MAX_BN + ((uint32_t)(q * 32) << 16);
     const int nchunks = p.BN / 32;
-    const int c_begin = ((warp - 2) >> 2) * (nchunks / 2), c_end = c_begin + nchunks / 2;
+    const int set = (warp - 2) >> 2; // which half of the tile's columns this warp drains
+    const int c_begin = set * (nchunks / 2), c_end = c_begin + nchunks / 2;
+    if (p.tma_store) {
+      // Converted rows go to a 128-byte-swizzled staging box (128 rows x 64 channels) and leave by
+      // ONE tiled TMA store per box: whole 128-byte lines, clipped at the tensor's edges by the TMA
+      // unit. (One 16-byte store per lane straight from registers touches 32 different lines per
+      // instruction, two instructions per 32-byte sector: those stores alone kept the load/store
+      // unit busy for more than half of the kernel on the layers with few K blocks per tile.)
+      // Warps that share a box meet at a named barrier. BN = 64: one box per tile shared by all
+      // eight warps, the two staging buffers alternate between tiles and ONE barrier per tile says
+      // both "this tile is written" and "the other buffer has been read" (the issuing thread waits
+      // for its previous store's read before it arrives). Otherwise the four warps of a column half
+      // own one buffer and BN / 128 boxes per tile, with a barrier before and after the writes.
+      const bool whole = p.BN == 64;
+      const int bar_id = whole ? 1 : 1 + set, bar_threads = whole ? 256 : 128;
+      const bool issuer = lane == 0 && warp == (whole ? 2 : 2 + 4 * set);
+      const uint32_t buf = staging + (whole ? (lt & 1u) : (uint32_t)set) * BOX_BYTES;
+      const int boxes = whole ? 1 : p.BN / 128;
+      const bool bf = p.epi.out_dtype == FB_DT_BFLOAT16;
+      // 32 accumulator columns of this thread's row -> fused chain -> 16-bit -> four 16-byte chunks of
+      // the row's 128-byte line in the staging box (chunk index XOR row: the 128-byte swizzle)
+      auto stage_chunk = [&](uint32_t (&raw)[32], int c, int box_col0) {
+        const int nc = no0 + c * 32;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+        if (row_ok && nc < p.Nout) epi_run32(p.epi, v, row_off, nc, min(32, p.Nout - nc));
+        const int chunk0 = ((c * 32 - box_col0) >> 3); // 0 or 4
+        const uint32_t row_addr = buf + (uint32_t)row * 128u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t wv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float lo = v[8 * j + 2 * e], hi = v[8 * j + 2 * e + 1];
+            if (bf) {
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(lo, hi);
+              wv[e] = *reinterpret_cast<uint32_t *>(&h2);
+            } else {
+              __half2 h2 = __floats2half2_rn(lo, hi);
+              wv[e] = *reinterpret_cast<uint32_t *>(&h2);
+            }
+          }
+          st_shared_v4(row_addr + (uint32_t)(((chunk0 + j) ^ (row & 7)) << 4), wv[0], wv[1], wv[2], wv[3]);
+        }
+      };
+      auto release_accumulator = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+      };
+      uint32_t raw_a[32], raw_b[32];
+      tmem_ld_32x32(taddr + c_begin * 32, raw_a);
+      if (whole) {
+        tmem_ld_wait();
+        release_accumulator();
+        if (warp == 2) TR_ADD(6);
+        stage_chunk(raw_a, c_begin, 0);
+        if (warp == 2) TR_ADD(7); // epilogue: convert, staging writes
+        fence_proxy_async(); // generic-proxy writes above, async-proxy reads below
+        if (issuer) tma_store_wait_read(); // frees the buffer the NEXT tile writes
+        if (warp == 2) TR_ADD(8);
+        named_barrier_sync(bar_id, bar_threads);
+        if (warp == 2) TR_ADD(9);
+        if (issuer) {
+          tma_store_4d(tmap_c, buf, no0, tw * p.bw, th * p.bh, tb * p.bn);
+          tma_store_commit();
+        }
+        continue;
+      }
+      // Two chunks per box; the TMEM load of the next chunk is in flight while this one is converted.
+      for (int bx = 0; bx < boxes; ++bx) {
+        const int box_col0 = (set * boxes + bx) * 64; // first channel of the box within the tile
+        const int c0 = c_begin + bx * 2;
+        tmem_ld_wait();
+        tmem_ld_32x32(taddr + (c0 + 1) * 32, raw_b);
+        if (issuer) tma_store_wait_read(); // the previous store has read this buffer
+        named_barrier_sync(bar_id, bar_threads);
+        if (warp == 2) TR_ADD(6); // epilogue: set-up + first barrier
+        stage_chunk(raw_a, c0, box_col0);
+        tmem_ld_wait();
+        if (bx + 1 < boxes) tmem_ld_32x32(taddr + (c0 + 2) * 32, raw_a);
+        else release_accumulator();
+        stage_chunk(raw_b, c0 + 1, box_col0);
+        if (warp == 2) TR_ADD(7); // epilogue: convert, staging writes
+        fence_proxy_async();
+        named_barrier_sync(bar_id, bar_threads);
+        if (warp == 2) TR_ADD(9); // epilogue: barrier
+        if (issuer) {
+          tma_store_4d(tmap_c, buf, no0 + box_col0, tw * p.bw, th * p.bh, tb * p.bn);
+          tma_store_commit();
+        }
+      }
+      continue;
+    }
 #pragma unroll 1
     for (int c = c_begin; c < c_end; ++c) {
       uint32_t raw[32];
@@ -111,13 +223,14 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, uint3
       }
     }
   }
+  if (p.tma_store && lane == 0 && (warp == 2 || warp == 6)) tma_store_wait_all(); // before the CTA's memory goes away
 }
 
 // The per-tap kernel runs one more warp than the halo kernel: a second TMA producer.
 constexpr int NUM_THREADS_TAP = NUM_THREADS + 32;
 __global__ void __launch_bounds__(NUM_THREADS_TAP, 1)
 conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    const ConvTcParams p) {
+                    const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int STAGES = p.stages;
@@ -142,6 +255,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.tma_store) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -229,7 +343,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (ok) tc_commit_elect(tfull_bar(acc));
     }
   } else {
-    conv_epilogue_warps(p, tmem_base, tfull_bar(0), tempty_bar(0), warp, lane);
+    conv_epilogue_warps(p, &tmap_c, smem_base + RING_BYTES_STAGED, tmem_base, tfull_bar(0), tempty_bar(0), warp, lane);
   }
   tc_fence_before();
   __syncthreads();
@@ -254,7 +368,7 @@ constexpr int HALO_BW = 8, HALO_BH = 16;
 constexpr int HALO_MAX_A_SLOTS = 4, HALO_MAX_B_STAGES = 12;
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const ConvTcParams p) {
+                         const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sb_base = smem_base + (uint32_t)(p.a_slots * p.a_slot_bytes);
@@ -285,6 +399,7 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.tma_store) tma_prefetch_desc(&tmap_c);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -327,13 +442,17 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
       const int w0 = tw * p.bw + p.org_w, h0 = th * p.bh + p.org_h, no0 = tno * p.BN;
       for (int cb = 0; cb < p.cblocks && ok; ++cb) {
+        TR_BEGIN;
         if (!mbar_wait_warp(a_empty(sa), pha ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        TR_ADD(0); // producer: waiting for a free patch slot
         if (leader) {
           mbar_expect_tx(a_full(sa), (uint32_t)p.S * patch_bytes);
           for (int ss = 0; ss < p.S; ++ss)
             tma_load_4d(smem_base + (uint32_t)(sa * p.a_slot_bytes) + (uint32_t)ss * patch_bytes, &tmap_a, a_full(sa),
                         cb * BK, w0 + ss, h0, tb);
         }
+        __syncwarp();
+        TR_ADD(1); // producer: expect + TMA issue
         sa = (sa + 1 == p.a_slots) ? 0 : sa + 1;
         pha ^= (sa == 0);
         if (!p.b_resident) {
@@ -362,11 +481,14 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
       const int acc = lt & 1;
       const uint32_t aph = (lt >> 1) & 1;
+      TR_BEGIN;
       if (!mbar_wait_warp(tempty0 + 8u * acc, aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+      TR_ADD(2); // MMA warp: waiting for a drained accumulator
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * MAX_BN;
       for (int cb = 0; cb < p.cblocks && ok; ++cb) {
         if (!mbar_wait_warp(a_full(sa), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        TR_ADD(3); // MMA warp: waiting for the patch to land
         tc_fence_after();
         const uint64_t ad = a_desc0 + (uint64_t)((uint32_t)(sa * p.a_slot_bytes) >> 4);
         int tr = 0, ts = 0;
@@ -398,13 +520,14 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
         }
         tc_commit_elect(a_empty(sa));
+        TR_ADD(4); // MMA warp: issuing the taps' MMAs
         sa = (sa + 1 == p.a_slots) ? 0 : sa + 1;
         pha ^= (sa == 0);
       }
       if (ok) tc_commit_elect(tfull0 + 8u * acc);
     }
   } else {
-    conv_epilogue_warps(p, tmem_base, tfull0, tempty0, warp, lane);
+    conv_epilogue_warps(p, &tmap_c, smem_base + RING_BYTES_STAGED, tmem_base, tfull0, tempty0, warp, lane);
   }
   tc_fence_before();
   __syncthreads();
@@ -553,6 +676,9 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
   }
   // Halo path: taps read shifted windows of one patch per channel block. Taken when the fixed
   // 8 x 16 tile wastes little of the image.
+  // 16-bit outputs leave through staged TMA stores; the staging tiles come out of the ring's space
+  p.tma_store = is16(out.dtype) ? 1 : 0;
+  const int ring_bytes = p.tma_store ? RING_BYTES_STAGED : RING_BYTES;
   bool halo = false;
   if (!v.pointwise_1x1 && v.R * v.S > 1 && v.dil_h == 1 && v.dil_w == 1 && v.R <= 7 && v.S <= 7) {
     const int64_t tiles = (int64_t)((v.W + HALO_BW - 1) / HALO_BW) * ((v.H + HALO_BH - 1) / HALO_BH) * v.N;
@@ -562,7 +688,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     // (494 against 431 on 56x56 C64), so it is taken only when the filter slice stays resident.
     const int64_t filter_bytes = (int64_t)p.cblocks * v.R * v.S * p.BN * BK * 2;
     const int64_t slot_bytes = (int64_t)v.S * HALO_BW * (HALO_BH + v.R - 1) * 128;
-    halo = halo && v.Nout <= p.BN && filter_bytes + 2 * slot_bytes <= RING_BYTES;
+    halo = halo && v.Nout <= p.BN && filter_bytes + 2 * slot_bytes <= ring_bytes;
   }
   if (halo) {
     p.bw = HALO_BW; p.bh = HALO_BH; p.bn = 1;
@@ -586,16 +712,16 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
   p.a_bytes = (uint32_t)p.rows * BK * 2;
   p.b_bytes = (uint32_t)p.BN * BK * 2;
   p.stage_bytes = A_BYTES + p.BN * BK * 2;
-  p.stages = std::min(MAX_STAGES, RING_BYTES / p.stage_bytes);
+  p.stages = std::min(MAX_STAGES, ring_bytes / p.stage_bytes);
   if (halo) {
     const int64_t filter_bytes = (int64_t)p.cblocks * v.R * v.S * p.b_bytes;
-    p.b_resident = p.tiles_nout == 1 && filter_bytes + 2 * p.a_slot_bytes <= RING_BYTES;
+    p.b_resident = p.tiles_nout == 1 && filter_bytes + 2 * p.a_slot_bytes <= ring_bytes;
     if (p.b_resident) {
-      p.a_slots = (int)std::min<int64_t>(HALO_MAX_A_SLOTS, (RING_BYTES - filter_bytes) / p.a_slot_bytes);
+      p.a_slots = (int)std::min<int64_t>(HALO_MAX_A_SLOTS, (ring_bytes - filter_bytes) / p.a_slot_bytes);
       p.b_stages = 1;
     } else {
       p.a_slots = 2;
-      p.b_stages = (int)std::min<int64_t>(HALO_MAX_B_STAGES, (RING_BYTES - 2 * p.a_slot_bytes) / p.b_bytes);
+      p.b_stages = (int)std::min<int64_t>(HALO_MAX_B_STAGES, (ring_bytes - 2 * p.a_slot_bytes) / p.b_bytes);
     }
   }
   p.out = optr;
@@ -621,7 +747,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
       }
     }
   }
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
   const char *why = "";
   {
     uint32_t box[4] = {BK, (uint32_t)p.bw, (uint32_t)(halo ? p.phh : p.bh), (uint32_t)p.bn};
@@ -634,6 +760,25 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     uint32_t wbox_d[4] = {64, 1, 1, BK};
     FB_REQUIRE(encode_tmap_2byte(&tmB, wptr, 4, w_dims, w_str, v.dgrad ? wbox_d : wbox_f, &why),
                FB_RUNTIME_FAILURE, why);
+    if (p.tma_store) {
+      // the output as (channels, W, H, N) -- or (channels, pixels, 1, 1) for a collapsed 1x1 layer --
+      // stored in boxes of 64 channels by the tile's pixel patch
+      const uint64_t oc = (uint64_t)out.dims[1];
+      uint64_t c_dims[4], c_str[3];
+      if (v.pointwise_1x1) {
+        const uint64_t pix = (uint64_t)v.N * v.H * v.W;
+        c_dims[0] = oc; c_dims[1] = pix; c_dims[2] = 1; c_dims[3] = 1;
+        c_str[0] = oc * 2; c_str[1] = pix * oc * 2; c_str[2] = pix * oc * 2;
+      } else {
+        c_dims[0] = oc; c_dims[1] = (uint64_t)v.W; c_dims[2] = (uint64_t)v.H; c_dims[3] = (uint64_t)v.N;
+        c_str[0] = oc * 2; c_str[1] = (uint64_t)v.W * oc * 2; c_str[2] = (uint64_t)v.H * v.W * oc * 2;
+      }
+      uint32_t cbox[4] = {64, (uint32_t)p.bw, (uint32_t)p.bh, (uint32_t)p.bn};
+      FB_REQUIRE(((uintptr_t)optr % 16) == 0, FB_INVALID_ARGUMENT, "conv_tcgen05: output buffer must be 16-byte aligned");
+      FB_REQUIRE(encode_tmap_2byte(&tmC, optr, 4, c_dims, c_str, cbox, &why), FB_RUNTIME_FAILURE, why);
+    } else {
+      tmC = tmA; // unused by the kernel
+    }
   }
   cudaError_t ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
@@ -643,11 +788,22 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_halo_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
     FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
                std::string("conv_halo_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
-    conv_halo_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+    conv_halo_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
     return FB_OK;
   }
-  conv_tcgen05_kernel<<<grid, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+  conv_tcgen05_kernel<<<grid, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
   return FB_OK;
 }
 
 } // namespace fb
+
+#ifdef FB_CONV_TRACE
+FB_EXPORT fb_status fb_debug_conv_trace(unsigned long long *out, int reset) {
+  cudaMemcpyFromSymbol(out, fb::g_conv_trace, sizeof(unsigned long long) * 32);
+  if (reset) {
+    unsigned long long z[32] = {0};
+    cudaMemcpyToSymbol(fb::g_conv_trace, z, sizeof(z));
+  }
+  return FB_OK;
+}
+#endif

@@ -695,7 +695,7 @@ int step_launches(const Plan &p, const Step &s) {
   if (s.kind == STEP_BATCHNORM) return (p.nodes[s.node].d.flags & FB_FLAG_NORM_TRAINING) ? 3 : 1;
   const bool wgrad = p.nodes[s.node].d.op == FB_OP_CONV_WGRAD;
   if (wgrad && s.engine == ENGINE_TCGEN05) return 2; // partial kernel + slice reduction
-  if (s.engine == ENGINE_TCGEN05_SPLIT) return 3;    // piece split of X, of W, convolution
+  if (s.engine == ENGINE_TCGEN05_SPLIT) return 2;    // piece split of X and W, convolution
   return s.split_k > 1 ? 2 : 1;
 }
 

@@ -27,7 +27,25 @@ def test_conv_fprop_c1_exact_config():
     g, ins, y = wl.conv_fprop_bias_relu(16, 64, 56, 56, 64, 3, 3, 1, F32)
     data = _inputs(ins, 0x5EED + 0, per={"bias": ("uniform", -0.1, 0.1)})
     check_graph(g, data)
-    assert g.numLaunches() == 1 and g.getWorkspaceSize() == 0  # conv+bias+relu is one kernel
+    # bf16 piece split of x and w, then ONE tensor-core kernel for conv + bias + relu
+    assert "conv_fprop_split_f32_tcgen05" in g.statistics()
+    assert g.numLaunches() == 2 and g.getWorkspaceSize() > 0
+
+
+def test_conv_fprop_f32_tensor_core_path_beats_fp32_fma_accuracy():
+    """The fp32 forward convolution on the tensor cores (three bf16 pieces per operand, TMEM
+    accumulation restarted per filter tap, chunks added in fp32 registers) against the float64
+    accumulating oracle: its worst error must stay below what a plain fp32 FMA chain of the same
+    length gives (about 4e-5 on these inputs), i.e. it is an fp32-grade result, not a bf16 one."""
+    from helpers import run_gpu
+    from oracle import fusilli_oracle as orc
+    g, ins, y = wl.conv_fprop_bias_relu(6, 128, 28, 36, 96, 3, 3, 1, F32)
+    data = _inputs(ins, 0x5EED, per={"bias": ("uniform", -0.1, 0.1)})
+    want = orc.execute(g, data)[y].astype(np.float64)
+    got = run_gpu(g, data)[y].astype(np.float64)
+    assert "conv_fprop_split_f32_tcgen05" in g.statistics()
+    # K = 9 * 128 products of U[-1,1] values per output, |y| up to ~50
+    assert np.abs(got - want).max() < 3e-5
 
 
 @pytest.mark.parametrize("shape", [

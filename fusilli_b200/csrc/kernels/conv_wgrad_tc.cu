@@ -320,7 +320,8 @@ bool wgrad_view(const Plan &p, const Step &s, WgradView &v) {
   v.pad_h = (int)d.padding[0]; v.pad_w = (int)d.padding[1];
   v.dil_h = (int)d.dilation[0]; v.dil_w = (int)d.dilation[1];
   if (v.C % 8 || v.Kout % 8 || v.C < 64 || v.Kout < 64) return false;
-  if ((int64_t)v.N * v.P * v.Q < 4096) return false;
+  // at least 16 patches of 64 pixels to reduce over (a rank's shard of the 7x7 layer at N = 256 / 8 is 1568 pixels)
+  if ((int64_t)v.N * v.P * v.Q < 1024) return false;
   return true;
 }
 

@@ -11,6 +11,8 @@
 //   norm_rows_kernel         one row per CTA, the row packed in registers, parameters through L1;
 //   norm_generic_kernel      any row length and layouts where scale/bias/Y are ordered
 //                            differently from X (re-reads the row from L2).
+#include <cstdlib>
+
 #include "../common.h"
 #include "sm100.cuh"
 
@@ -406,9 +408,10 @@ static bool launch_staged(const NormParams &p, int sm_count, cudaStream_t st) {
 template <typename T, typename P>
 static bool launch_rows(const NormParams &p, int sm_count, cudaStream_t st) {
   constexpr int N = 16 / sizeof(T);
-  // LayerNorm: the staged kernel (scale and bias in registers); RMSNorm has half the parameter
-  // traffic and is faster on the one-row-per-CTA kernel below, which runs more warps per SM
-  if (!p.is_rms && launch_staged<T, P>(p, sm_count, st)) return true;
+  // Many long rows: the staged kernel (rows through a bulk-copy ring, parameters in registers) for both
+  // norms. Measured on 32768 x 8192 bf16 with the host's enqueue latency hidden: LayerNorm 0.177 ms,
+  // RMSNorm 0.180 ms staged against 0.188 ms on the one-row-per-CTA kernel below.
+  if (launch_staged<T, P>(p, sm_count, st)) return true;
   const int blocks = (int)std::min<int64_t>(p.batch, (int64_t)sm_count * 64);
   if (p.row % (128 * N) == 0 && p.row / (128 * N) <= 8) {
     switch (p.row / (128 * N)) {

@@ -11,5 +11,6 @@
 #include "fusilli/nodes.h"
 #include "fusilli/backend.h"
 #include "fusilli/graph.h"
+#include "fusilli/comm.h"
 
 #endif // FUSILLI_H

@@ -221,6 +221,46 @@ TEST_CASE("conv wgrad plan asks for a workspace and refuses to run without it", 
   REQUIRE(at(5, 9, 1, 0) == float(n * hw * (hw - 1)));
 }
 
+TEST_CASE("Comm: the fp32 weight-gradient partial lands in the exchange buffer and is summed and rounded there", "[comm]") {
+  // One rank (world = 1) exercises the whole C++ path of a sharded run: the graph declares its dW as fp32
+  // and binds it INTO the communicator's buffer, the fused sum rounds it once to bf16 in the same buffer.
+  const int64_t n = 8, c = 64, hw = 16, kk = 64;
+  const size_t elems = kk * c * 9;
+  FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));
+  FUSILLI_REQUIRE_ASSIGN(Comm comm, Comm::create(handle, /*rank=*/0, /*world=*/1, elems * 4 + elems * 2));
+  REQUIRE(comm.rank() == 0);
+  REQUIRE(comm.world() == 1);
+  REQUIRE(comm.bufferBytes() >= elems * 6);
+  Graph g;
+  g.setName("cpp_wgrad_comm").setIODataType(DataType::BFloat16).setComputeDataType(DataType::Float).setIntermediateDataType(DataType::Float);
+  auto dyT = g.tensor(TensorAttr().setName("dy").setDim({n, kk, hw, hw}).setStride({kk * hw * hw, 1, kk * hw, kk}));
+  auto xT = g.tensor(TensorAttr().setName("x").setDim({n, c, hw, hw}).setStride({c * hw * hw, 1, c * hw, c}));
+  ConvWGradAttr attr;
+  attr.setName("wgrad").setPadding({1, 1}).setStride({1, 1}).setDilation({1, 1});
+  auto dwT = g.convWGrad(dyT, xT, attr);
+  dwT->setOutput(true).setDataType(DataType::Float).setDim({kk, c, 3, 3}).setStride({c * 9, 1, c * 3, c});
+  FUSILLI_REQUIRE_OK(g.validate());
+  FUSILLI_REQUIRE_OK(g.compile(handle, /*remove=*/true));
+  FUSILLI_REQUIRE_ASSIGN(auto ws, g.getWorkspaceSize());
+  FUSILLI_REQUIRE_ASSIGN(auto dyBuf, allocateBufferOfType(handle, dyT, DataType::BFloat16, 1.0));
+  FUSILLI_REQUIRE_ASSIGN(auto xBuf, allocateBufferOfType(handle, xT, DataType::BFloat16, 1.0));
+  FUSILLI_REQUIRE_ASSIGN(auto dwView, comm.view(0, elems * 4));
+  Graph::VariantPack pack = {{dyT, dyBuf}, {xT, xBuf}, {dwT, dwView}};
+  FUSILLI_REQUIRE_ASSIGN(auto wsBuf, allocateWorkspace(handle, ws));
+  FUSILLI_REQUIRE_OK(g.execute(handle, pack, wsBuf));
+  FUSILLI_REQUIRE_OK(comm.sumFused(0, elems, elems * 4, DataType::BFloat16));
+  FUSILLI_REQUIRE_ASSIGN(auto outView, comm.view(elems * 4, elems * 2));
+  std::vector<bf16> dw;
+  FUSILLI_REQUIRE_OK(outView->read(handle, dw));
+  REQUIRE(dw.size() == elems);
+  auto at = [&](int64_t ki, int64_t ci, int64_t r, int64_t s) { return float(dw[((ki * 3 + r) * 3 + s) * c + ci]); };
+  REQUIRE(at(0, 0, 1, 1) == float(n * hw * hw));
+  REQUIRE(at(63, 63, 0, 0) == float(n * (hw - 1) * (hw - 1)));
+  // ranges that overlap or leave the buffer are refused before anything is launched
+  REQUIRE(comm.sumFused(0, elems, elems * 2, DataType::BFloat16).getCode() == ErrorCode::InvalidArgument);
+  REQUIRE(isError(comm.view(elems * 6, 4096)));
+}
+
 TEST_CASE("one plan with a dynamic batch serves channels-last buffers of several batch sizes", "[dynamic]") {
   const int64_t n = 8, c = 64, hw = 16, kk = 64;
   FUSILLI_REQUIRE_ASSIGN(Handle handle, Handle::create(kDefaultBackend));

@@ -266,3 +266,16 @@ def test_matmul_batch_broadcast_by_a_divisor_builds_a_plan():
     g.validate()
     assert c.dim == [4, 8, 8]
     assert runtime.lib().fb_plan_check(g.compileToArtifact(), len(g.compileToArtifact())) == 0
+
+
+def test_norm_on_a_batch_inner_or_padded_tensor_is_refused_at_plan_build():
+    """The row kernels walk a sample as one dense run of prod(dims[1:]) elements. The front ends only
+    admit contiguous or channels-last tensors; a graph that reaches the C ABI with another layout (here:
+    strides changed after validation) is refused when the plan is built, not run on the wrong bytes."""
+    for strides in ([1, 64], [1024 + 8, 1]):   # batch innermost; padded rows
+        g, ins, y = wl.rmsnorm_infer(64, 1024, DataType.Float)
+        ins["x"].stride = list(strides)
+        with pytest.raises(FusilliError) as e:
+            g.compileToArtifact()
+        assert e.value.code == ErrorCode.NotImplemented
+        assert "dense with the batch dim outermost" in e.value.message

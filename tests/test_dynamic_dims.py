@@ -316,3 +316,48 @@ def test_workspace_of_the_representative_shape_bounds_larger_shapes():
     with pytest.raises(FusilliError) as e:
         g.execute(handle, pack, ws)
     assert e.value.code == ErrorCode.InvalidArgument and "Workspace buffer too small" in e.value.message
+
+
+@pytest.mark.gpu
+def test_shape_cache_eviction_under_concurrent_callers():
+    """More distinct shapes than the per-plan cache holds (64), from several threads at once: a caller
+    keeps its specialised plan alive while another thread's new shape drops the cached set, so every
+    query returns the size a fresh specialisation of that shape gives (ctypes releases the GIL: the
+    calls really overlap)."""
+    import threading
+    g, ins, y = wl.rmsnorm_infer(64, 1024)
+    flag_dynamic(g, 0, ("gamma",))
+    handle = fz.Handle.create(fz.Backend.CUDA)
+    g.compile(handle)
+    lib = runtime.lib()
+    n = len(g._arg_tensors)
+    names = [t.name for t in g._arg_tensors]
+    errors = []
+
+    def dims_for(rows):
+        d = (ctypes.c_int64 * (n * 8))(*([1] * (n * 8)))
+        for i, t in enumerate(g._arg_tensors):
+            logical = list(t.dim)
+            if t.hasDynamicDims():
+                logical[0] = rows
+            for k, v in enumerate(logical):
+                d[i * 8 + k] = v
+        return d
+
+    def worker(seed):
+        rng = np.random.default_rng(seed)
+        for _ in range(400):
+            rows = int(rng.integers(1, 200))
+            out = ctypes.c_size_t(12345)
+            st = lib.fb_plan_workspace_size_shaped(g._plan, dims_for(rows), n, ctypes.byref(out))
+            if st != 0 or out.value != 0:   # a row norm needs no workspace at any batch size
+                errors.append((rows, st, out.value))
+
+    threads = [threading.Thread(target=worker, args=(s,)) for s in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors[:5]
+    assert names  # the plan is still usable afterwards
+    assert g.getWorkspaceSize() == 0

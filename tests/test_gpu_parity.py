@@ -63,6 +63,23 @@ def test_conv_resnet_layers_bf16_fprop_dgrad_wgrad(shape):
     g, ins, _ = wl.conv_wgrad(n, c, h, w, k, r, s, pad, BF16)
     check_graph(g, _inputs(ins, 3, per={"dy": dy_dist, "x": x_dist}))
 @pytest.mark.parametrize("shape", [
+    (32, 512, 7, 7, 512, 3, 3, 1),    # one rank's shard of the 7x7 layer on 8 GPUs: 1568 pixels, 25 ragged patches
+    (64, 512, 7, 7, 512, 3, 3, 1),    # ... on 4 GPUs
+    (32, 256, 14, 14, 1024, 1, 1, 0),  # the 14x14 1x1 layer's shard on 8 GPUs
+    (21, 64, 7, 7, 64, 3, 3, 1),      # 1029 pixels: just above the tensor-core kernel's threshold
+])
+def test_conv_wgrad_small_pixel_counts_on_tensor_cores(shape):
+    """Weight gradients whose reduction is only a few thousand pixels (what a rank sees when the
+    benchmark's batch is split over 4 or 8 GPUs) still take the tensor-core kernel."""
+    n, c, h, w, k, r, s, pad = shape
+    g, ins, _ = wl.conv_wgrad(n, c, h, w, k, r, s, pad, BF16)
+    check_graph(g, _inputs(ins, 17, per={"dy": ("normal", 0.0, 0.01), "x": ("normal", 0.0, 0.05)}))
+    assert "conv_wgrad_tcgen05" in g.statistics()
+    g, ins, _ = wl.conv_wgrad(n, c, h, w, k, r, s, pad, BF16, dw_dtype=F32)   # the fp32 partial a rank contributes
+    check_graph(g, _inputs(ins, 18, per={"dy": ("normal", 0.0, 0.01), "x": ("normal", 0.0, 0.05)}))
+
+
+@pytest.mark.parametrize("shape", [
     (2, 96, 30, 24, 160, 3, 3, 1),   # ragged channel block and ragged output-channel tile
     (1, 64, 32, 32, 64, 5, 5, 2),    # 5x5 taps, resident filter
     (1, 64, 34, 34, 128, 3, 3, 0),   # no padding: output 32x32

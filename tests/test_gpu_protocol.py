@@ -162,3 +162,41 @@ def test_reexecution_is_stable():
     first = run_gpu(g, data, h, repeat=1)[out]
     again = run_gpu(g, data, h, repeat=3)[out]
     assert np.array_equal(first, again)  # deterministic kernels: bitwise repeatable
+
+
+@pytest.mark.gpu
+def test_padded_leading_stride_needs_a_buffer_that_covers_the_padding():
+    """A matmul operand whose leading stride exceeds its row length (rows padded to 136 elements for a
+    128-wide A; reachable through the C ABI only): the size check counts one past the last element's offset, so a buffer of just
+    prod(dims) elements is refused and the padded one computes the right product."""
+    import ctypes
+    from fusilli_b200.graph import DataType, ErrorCode, FusilliError, TensorAttr, contiguousStride
+    from oracle import fusilli_oracle as orc
+    m, k, n, lda = 256, 128, 192, 136
+    g = fz.Graph()
+    g.setName("mm_padded").setIODataType(DataType.BFloat16).setComputeDataType(DataType.Float).setIntermediateDataType(DataType.Float)
+    a = g.tensor(TensorAttr().setName("a").setDim([m, k]).setStride([k, 1]))
+    b = g.tensor(TensorAttr().setName("b").setDim([k, n]).setStride(contiguousStride([k, n])))
+    c = g.matmul(a, b, fz.MatmulAttr().setName("mm"))
+    c.setName("c").setOutput(True)
+    g.validate()
+    a.stride = [lda, 1]   # the front ends only admit dense layouts; the C ABI takes padded rows
+    handle = fz.Handle.create(fz.Backend.CUDA)
+    g.compile(handle)
+    g.getWorkspaceSize()
+    rng = np.random.default_rng(5)
+    a_pad = orc.to_storage(rng.normal(0, 0.5, m * lda).astype(np.float32), DataType.BFloat16)
+    b_val = orc.to_storage(rng.normal(0, 0.5, k * n).astype(np.float32), DataType.BFloat16)
+    need = (m - 1) * lda + k
+    bb = fz.Buffer.allocate(handle, [b_val.size], b_val)
+    cb = fz.Buffer.allocate(handle, [m * n], np.zeros(m * n, np.uint16))
+    short = fz.Buffer.allocate(handle, [m * k], a_pad[: m * k])
+    with pytest.raises(FusilliError) as e:
+        g.execute(handle, {a: short, b: bb, c: cb}, None)
+    assert e.value.code == ErrorCode.InvalidArgument and "needs" in e.value.message
+    ab = fz.Buffer.allocate(handle, [need], a_pad[:need])
+    g.execute(handle, {a: ab, b: bb, c: cb}, None)
+    got = orc.from_storage(cb.read(handle, np.uint16), DataType.BFloat16).reshape(m, n)
+    a_log = orc.from_storage(a_pad, DataType.BFloat16).reshape(m, lda)[:, :k].astype(np.float64)
+    want = a_log @ orc.from_storage(b_val, DataType.BFloat16).reshape(k, n).astype(np.float64)
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2 * min(1.0, np.abs(want).max()))

@@ -24,11 +24,14 @@ using namespace sm100;
 
 namespace {
 
-constexpr int BM = 128, KPIX = 64, A_STAGES = 3, B_STAGES = 4, MAX_BN = 256;
-constexpr int A_STAGE_BYTES = BM * KPIX * 2;     // 16 KB: two 64-channel halves of 64 pixels
-constexpr int B_STAGE_BYTES = MAX_BN * KPIX * 2; // 32 KB
-constexpr int HALF = 64 * KPIX * 2;              // one [64 pixels][64 channels] box
-constexpr int SMEM_BYTES = A_STAGES * A_STAGE_BYTES + B_STAGES * B_STAGE_BYTES + 1024 + 256;
+constexpr int BM = 128, KPIX = 64, MAX_BN = 256;
+constexpr int HALF = 64 * KPIX * 2;              // one [64 pixels][64 channels] box, 8 KB
+// The dY ring gets 48 KB and the X ring 128 KB; a stage is as large as the layer's tiles need
+// (dY: one or two boxes; X: up to four), so narrow layers keep more loads in flight: 6 + 12 stages
+// of 8 KB on a 1x1 C64 layer against 3 + 4 stages of 16 / 32 KB on the wide ones.
+constexpr int A_RING_BYTES = 3 * BM * KPIX * 2, B_RING_BYTES = 4 * MAX_BN * KPIX * 2;
+constexpr int MAX_A_STAGES = 6, MAX_B_STAGES = 12;
+constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + 1024 + 512;
 constexpr int NUM_THREADS = 192;
 constexpr int B_PRODUCERS = 4; // warps 0, 3, 4, 5 take every fourth B stage each
 constexpr int TMEM_COLS = 512;
@@ -42,6 +45,7 @@ struct WgradTcParams {
   int32_t patches_total, patches_per_slice, slices;
   int32_t k_tiles, c_tiles, ngroups, taps_per_group, BN, a_halves;
   int32_t tpack;            // filter taps that share one B stage and one MMA (tpack * BN <= 256)
+  int32_t a_stages, b_stages, a_stage_bytes, b_stage_bytes;
   float *partial;           // [slices][Kout][R*S][C] fp32
   uint32_t *err;
 };
@@ -51,13 +55,15 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
                           const WgradTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sb_base = smem_base + A_STAGES * A_STAGE_BYTES;
-  const uint32_t bar_base = sb_base + B_STAGES * B_STAGE_BYTES;
+  const int A_STAGES = p.a_stages, B_STAGES = p.b_stages;
+  const uint32_t A_STAGE_BYTES = (uint32_t)p.a_stage_bytes, B_STAGE_BYTES = (uint32_t)p.b_stage_bytes;
+  const uint32_t sb_base = smem_base + A_RING_BYTES;
+  const uint32_t bar_base = sb_base + B_RING_BYTES;
   auto a_full = [&](int s) { return bar_base + 8u * s; };
-  auto a_empty = [&](int s) { return bar_base + 8u * (A_STAGES + s); };
-  auto b_full = [&](int s) { return bar_base + 8u * (2 * A_STAGES + s); };
-  auto b_empty = [&](int s) { return bar_base + 8u * (2 * A_STAGES + B_STAGES + s); };
-  const uint32_t acc_full = bar_base + 8u * (2 * A_STAGES + 2 * B_STAGES);
+  auto a_empty = [&](int s) { return bar_base + 8u * (MAX_A_STAGES + s); };
+  auto b_full = [&](int s) { return bar_base + 8u * (2 * MAX_A_STAGES + s); };
+  auto b_empty = [&](int s) { return bar_base + 8u * (2 * MAX_A_STAGES + MAX_B_STAGES + s); };
+  const uint32_t acc_full = bar_base + 8u * (2 * MAX_A_STAGES + 2 * MAX_B_STAGES);
   const uint32_t tmem_slot = acc_full + 8u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -105,7 +111,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       const int w0 = tw * p.bw, h0 = th * p.bh, n0 = tb * p.bn;
       if (!mbar_wait_warp(a_empty(sa_i), pha ^ 1, p.err, ERR_WAIT_EMPTY)) break;
       mbar_expect_tx_elect(a_full(sa_i), a_bytes);
-      const uint32_t sa = smem_base + sa_i * A_STAGE_BYTES;
+      const uint32_t sa = smem_base + (uint32_t)sa_i * A_STAGE_BYTES;
       for (int hh = 0; hh < p.a_halves; ++hh)
         tma_load_4d_elect(sa + hh * HALF, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
       sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
@@ -137,7 +143,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
           if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
           mbar_expect_tx_elect(b_full(sb_i), (uint32_t)nt * b_bytes);
         }
-        const uint32_t sb = sb_base + sb_i * B_STAGE_BYTES;
+        const uint32_t sb = sb_base + (uint32_t)sb_i * B_STAGE_BYTES;
         for (int u = 0; u < nt; ++u) {
           if (mine)
             for (int i = 0; i < p.BN / 64; ++i)
@@ -179,13 +185,13 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
     bool ok = true;
     for (int pi = 0; pi < npatch && ok; ++pi) {
       if (!mbar_wait_warp(a_full(sa_i), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-      const uint64_t ad = a_desc0 + (uint64_t)((sa_i * A_STAGE_BYTES) >> 4);
+      const uint64_t ad = a_desc0 + (uint64_t)(((uint32_t)sa_i * A_STAGE_BYTES) >> 4);
       for (int t = 0; t < ntaps; t += p.tpack) {
         const int nt = min(p.tpack, ntaps - t);
         const uint32_t idesc = nt == 1 ? idesc_n[0] : (nt == 2 ? idesc_n[1] : (nt == 3 ? idesc_n[2] : idesc_n[3]));
         if (!mbar_wait_warp(b_full(sb_i), phb, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t bd = b_desc0 + (uint64_t)((sb_i * B_STAGE_BYTES) >> 4);
+        const uint64_t bd = b_desc0 + (uint64_t)(((uint32_t)sb_i * B_STAGE_BYTES) >> 4);
 #pragma unroll
         for (int k = 0; k < KPIX / 16; ++k)
           tc_mma_f16_elect(tmem_base + t * p.BN, ad + (uint64_t)((k * 2048) >> 4), bd + (uint64_t)((k * 2048) >> 4),
@@ -412,6 +418,10 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
   p.BN = t.BN;
   p.a_halves = (v.Kout - 0 > 64) ? 2 : 1;
   p.tpack = std::max(1, std::min(4, MAX_BN / t.BN));
+  p.a_stage_bytes = p.a_halves * HALF;
+  p.b_stage_bytes = std::min(p.tpack, t.taps_per_group) * (t.BN / 64) * HALF;
+  p.a_stages = std::min(MAX_A_STAGES, A_RING_BYTES / p.a_stage_bytes);
+  p.b_stages = std::min(MAX_B_STAGES, B_RING_BYTES / p.b_stage_bytes);
   p.partial = reinterpret_cast<float *>(cx.workspace + s.scratch_offset);
   p.err = cx.dev->error_word;
   CUtensorMap tmDy, tmX;

@@ -1,16 +1,17 @@
-"""Batch sharding of the hot path across ranks (one process per GPU).
+"""Host-side arithmetic of batch sharding across ranks (one process per GPU): which slab of the
+outermost extent a rank owns, and torch.distributed forms of the gather / weight-gradient sum that run
+on any backend.
 
-Every benchmarked op shards over its outermost extent with no data-path exchange
-(images for conv fprop/dgrad, matrices for batched matmul, batch*heads for SDPA, rows
-for norms and row reductions); the shards are dense leading slabs of the full tensors,
-so gathering the outputs is one all_gather on the leading dimension. The only real
-exchange is wgrad: each rank reduces over its own images and the partial filter
-gradients are summed (fp32) across ranks before the final rounding.
+Every benchmarked op shards over its outermost extent with no data-path exchange (images for conv
+fprop/dgrad, matrices for batched matmul, batch for SDPA, rows for norms and row reductions); the
+shards are dense leading slabs of the full tensors. The only real exchange is wgrad: each rank reduces
+over its own images and the partial filter gradients are summed (fp32) across ranks before the final
+rounding. On GPUs that sum and the output gather are `fusilli_b200.comm.Comm` (the C ABI's fb_comm_*:
+fused peer-memory kernel, NCCL all-reduce, NCCL all-gather); the torch.distributed helpers below state
+the same operations for the CPU tests (gloo, world size 2, results from the CPU oracle).
 
 The reference has no multi-device code (one Handle = one device,
-include/fusilli/backend/runtime.h:19-24); this is the harness around per-device
-Handles that BASELINE's multi-GPU configs ask for. Works with any torch.distributed
-backend (nccl on GPUs, gloo in the CPU tests).
+include/fusilli/backend/runtime.h:19-24).
 """
 from __future__ import annotations
 

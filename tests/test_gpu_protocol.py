@@ -200,3 +200,25 @@ def test_padded_leading_stride_needs_a_buffer_that_covers_the_padding():
     a_log = orc.from_storage(a_pad, DataType.BFloat16).reshape(m, lda)[:, :k].astype(np.float64)
     want = a_log @ orc.from_storage(b_val, DataType.BFloat16).reshape(k, n).astype(np.float64)
     np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2 * min(1.0, np.abs(want).max()))
+
+
+@pytest.mark.gpu
+def test_bound_graph_runs_like_execute():
+    """Graph.bind marshals the buffers once; run() must produce what execute() produces, apply the
+    same variant-pack checks at bind time, and stay valid over repeated runs."""
+    g, ins, out = wl.matmul_bias(2, 128, 128, 64)
+    rng = np.random.default_rng(9)
+    data = {t: make_input(t, rng, ("normal", 0.0, 0.5)) for t in ins.values()}
+    handle = fz.Handle.create(fz.Backend.CUDA)
+    want = run_gpu(g, data, handle)[out]
+    pack = {t: fz.Buffer.allocate(handle, [a.size], a) for t, a in data.items()}
+    pack[out] = fz.Buffer.allocate(handle, [want.size], np.zeros(want.size, want.dtype))
+    bound = g.bind(handle, pack, None)
+    for _ in range(3):
+        bound.run()
+    assert np.array_equal(pack[out].read(handle, want.dtype), want)
+    missing = dict(pack)
+    del missing[out]
+    with pytest.raises(FusilliError) as e:
+        g.bind(handle, missing, None)
+    assert e.value.code == ErrorCode.VariantPackError

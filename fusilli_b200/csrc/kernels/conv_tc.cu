@@ -76,6 +76,7 @@ struct ConvTcParams {
   void *out;
   int64_t out_sn, out_sh, out_sw;        // element strides of the output (channel stride 1)
   int32_t tma_store;                     // 16-bit output: stage tiles in shared memory, store them by TMA
+  int32_t nacc, nacc_log2, acc_cols;     // TMEM accumulator ring: 2 or 4 tiles, acc_cols columns apart
   uint32_t *err;
   TcEpilogue epi;
 };
@@ -95,8 +96,8 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
   for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
     const int tp = tile % tiles_pix, tno = tile / tiles_pix;
     const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
-    const int acc = lt & 1;
-    const uint32_t aph = (lt >> 1) & 1;
+    const int acc = (int)(lt & (uint32_t)(p.nacc - 1));
+    const uint32_t aph = (lt >> p.nacc_log2) & 1;
     TR_BEGIN;
     if (!mbar_wait(tfull0 + 8u * acc, aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     if (warp == 2) TR_ADD(5); // epilogue: waiting for a finished accumulator
@@ -107,7 +108,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
     const bool row_ok = row < p.rows && w < p.W && h < p.H && n < p.N;
     const int64_t row_off = (int64_t)n * p.out_sn + (int64_t)h * p.out_sh + (int64_t)w * p.out_sw;
     const int no0 = tno * p.BN;
-    const uint32_t taddr = tmem_base + acc * MAX_BN + ((uint32_t)(q * 32) << 16);
+    const uint32_t taddr = tmem_base + acc * p.acc_cols + ((uint32_t)(q * 32) << 16);
     const int nchunks = p.BN / 32;
     const int set = (warp - 2) >> 2; // which half of the tile's columns this warp drains
     const int c_begin = set * (nchunks / 2), c_end = c_begin + nchunks / 2;
@@ -368,7 +369,9 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 // a ring, one (tap, channel block) box per step.
 constexpr int HALO_BW = 8, HALO_BH = 16;
 constexpr int HALO_MAX_A_SLOTS = 4, HALO_MAX_B_STAGES = 12;
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// The halo kernel's eleventh warp is a second MMA issuer (resident filter only).
+constexpr int NUM_THREADS_HALO = NUM_THREADS + 32;
+__global__ void __launch_bounds__(NUM_THREADS_HALO, 1)
 conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -380,8 +383,8 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   auto b_full = [&](int s) { return bar_base + 8u * (2 * HALO_MAX_A_SLOTS + s); };
   auto b_empty = [&](int s) { return bar_base + 8u * (2 * HALO_MAX_A_SLOTS + HALO_MAX_B_STAGES + s); };
   const uint32_t tfull0 = bar_base + 8u * (2 * HALO_MAX_A_SLOTS + 2 * HALO_MAX_B_STAGES);
-  const uint32_t tempty0 = tfull0 + 16u;
-  const uint32_t tmem_slot = tfull0 + 32u;
+  const uint32_t tempty0 = tfull0 + 32u; // up to four accumulators
+  const uint32_t tmem_slot = tfull0 + 64u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int taps = p.R * p.S;
 
@@ -394,7 +397,7 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       mbar_init(b_full(s), 1);
       mbar_init(b_empty(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < 4; ++a) {
       mbar_init(tfull0 + 8u * a, 1);
       mbar_init(tempty0 + 8u * a, 8);
     }
@@ -470,29 +473,65 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       }
     }
-  } else if (warp == 1) {
-    const bool leader = elect_one();
+  } else if (warp == 1 || warp == NUM_THREADS / 32) {
+    // MMA issue. The tensor pipe queues only a few instructions: while the issuing warp sits in the
+    // barrier waits between two tiles (a few hundred cycles even when both are already complete) the
+    // pipe runs dry, and a 128 x 64 x 16 MMA lasts only 48 clk. With the filter resident, two warps
+    // therefore issue alternate tiles (each its own accumulators and patch slots), so that one of
+    // them is always issuing; MMAs of different tiles may interleave in the pipe. With a streamed
+    // filter the ring is consumed in tile order and warp 1 issues alone.
+    const bool two = p.b_resident != 0;
+    const uint32_t first = (two && warp != 1) ? 1u : 0u, step = two ? 2u : 1u;
     const uint32_t idesc = make_idesc_f16(BM, p.BN, p.ab_format, 0, p.dgrad);
     const uint32_t b_lbo = p.dgrad ? 64 * BK * 2 : 16, b_kstep = p.dgrad ? 2048 : 32;
     const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
     const uint64_t b_desc0 = make_smem_desc(sb_base, b_lbo, 1024);
-    bool ok = true;
-    if (p.b_resident) ok = mbar_wait_warp(b_full(0), 0, p.err, ERR_WAIT_FULL);
-    int sa = 0, sbs = 0;
-    uint32_t pha = 0, phb = 0, lt = 0;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
-      const int acc = lt & 1;
-      const uint32_t aph = (lt >> 1) & 1;
+    bool ok = warp == 1 || two;
+    const bool lean = p.b_resident && p.R == 3 && p.S == 3;
+    const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+    uint32_t a_off[9]; // descriptor offset (16-byte units) of each tap's window within a patch slot
+#pragma unroll
+    for (int t = 0; t < 9; ++t) {
+      const int tr = t / 3, ts = t % 3;
+      const int rr = p.dgrad ? 2 - tr : tr, ss = p.dgrad ? 2 - ts : ts;
+      a_off[t] = ((uint32_t)ss * patch_bytes + (uint32_t)rr * 1024u) >> 4;
+    }
+    if (ok && p.b_resident) ok = mbar_wait_warp(b_full(0), 0, p.err, ERR_WAIT_FULL);
+    int sbs = 0;
+    uint32_t phb = 0;
+    for (uint32_t lt = first; ok; lt += step) {
+      const int64_t tile = (int64_t)blockIdx.x + (int64_t)lt * gridDim.x;
+      if (tile >= p.total_tiles) break;
+      const int acc = (int)(lt & (uint32_t)(p.nacc - 1));
+      const uint32_t aph = (lt >> p.nacc_log2) & 1;
+      // patch slot and phase of this tile's first channel block (blocks are numbered through the tiles)
+      const uint32_t blk0 = lt * (uint32_t)p.cblocks;
+      int sa = (int)(blk0 % (uint32_t)p.a_slots);
+      uint32_t pha = (blk0 / (uint32_t)p.a_slots) & 1u;
       TR_BEGIN;
       if (!mbar_wait_warp(tempty0 + 8u * acc, aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
       TR_ADD(2); // MMA warp: waiting for a drained accumulator
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * MAX_BN;
+      const uint32_t d_tmem = tmem_base + acc * p.acc_cols;
       for (int cb = 0; cb < p.cblocks && ok; ++cb) {
         if (!mbar_wait_warp(a_full(sa), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         TR_ADD(3); // MMA warp: waiting for the patch to land
         tc_fence_after();
         const uint64_t ad = a_desc0 + (uint64_t)((uint32_t)(sa * p.a_slot_bytes) >> 4);
+        if (lean) {
+          // 3 x 3 taps, resident filter: the 36 MMAs straight-line, window and tap offsets from registers.
+          // The issue rate matters: each instruction lasts 48 clk on a 64-channel layer and only a few
+          // are queued, so address arithmetic between two of them is tensor time lost.
+          const uint32_t a_lo = (uint32_t)ad, b_lo = (uint32_t)b_desc0 + (uint32_t)cb * 9u * (p.b_bytes >> 4);
+#pragma unroll
+          for (int t = 0; t < 9; ++t) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+              tc_mma_f16_elect(d_tmem, ((uint64_t)a_hi << 32) | (a_lo + a_off[t] + (uint32_t)(k * 2)),
+                               ((uint64_t)b_hi << 32) | (b_lo + (uint32_t)t * (p.b_bytes >> 4) + (uint32_t)k * (b_kstep >> 4)),
+                               idesc, (cb > 0 || t > 0 || k > 0) ? 1u : 0u);
+          }
+        } else {
         int tr = 0, ts = 0;
         for (int t = 0; t < taps; ++t) {
           uint64_t bd;
@@ -511,8 +550,8 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           for (int k = 0; k < BK / 16; ++k)
             tc_mma_f16_elect(d_tmem, aw + (uint64_t)((k * 32) >> 4), bd + (uint64_t)((k * b_kstep) >> 4), idesc,
                              (cb > 0 || t > 0 || k > 0) ? 1u : 0u);
-          if (!p.b_resident) tc_commit_elect(b_empty(sbs));
           if (!p.b_resident) {
+            tc_commit_elect(b_empty(sbs));
             sbs = (sbs + 1 == p.b_stages) ? 0 : sbs + 1;
             phb ^= (sbs == 0);
           }
@@ -520,6 +559,7 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             ts = 0;
             ++tr;
           }
+        }
         }
         tc_commit_elect(a_empty(sa));
         TR_ADD(4); // MMA warp: issuing the taps' MMAs
@@ -701,6 +741,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
   // 8 x 16 tile wastes little of the image.
   // 16-bit outputs leave through staged TMA stores; the staging tiles come out of the ring's space
   p.tma_store = is16(out.dtype) ? 1 : 0;
+  p.nacc = 2; p.nacc_log2 = 1; p.acc_cols = MAX_BN;
   const int ring_bytes = p.tma_store ? RING_BYTES_STAGED : RING_BYTES;
   bool halo = false;
   if (!v.pointwise_1x1 && v.R * v.S > 1 && v.dil_h == 1 && v.dil_w == 1 && v.R <= 7 && v.S <= 7) {
@@ -721,6 +762,8 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     p.org_w = v.dgrad ? v.pad_w - (v.S - 1) : -v.pad_w;
     p.org_h = v.dgrad ? v.pad_h - (v.R - 1) : -v.pad_h;
     p.a_slot_bytes = v.S * HALO_BW * p.phh * 128; // S column-shifted patches of 8 x phh pixels
+    // two accumulators per issuing warp, so that neither waits for the tile it just finished to drain
+    if (p.BN <= 128) { p.nacc = 4; p.nacc_log2 = 2; p.acc_cols = 128; }
   }
   p.rows = p.bw * p.bh * p.bn;
   if (!v.dgrad) { p.off_h = -v.pad_h; p.off_w = -v.pad_w; p.step_h = v.dil_h; p.step_w = v.dil_w; }
@@ -811,7 +854,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_halo_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
     FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
                std::string("conv_halo_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
-    conv_halo_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
+    conv_halo_tcgen05_kernel<<<grid, NUM_THREADS_HALO, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
     return FB_OK;
   }
   conv_tcgen05_kernel<<<grid, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);

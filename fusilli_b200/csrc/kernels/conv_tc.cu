@@ -77,6 +77,7 @@ struct ConvTcParams {
   int64_t out_sn, out_sh, out_sw;        // element strides of the output (channel stride 1)
   int32_t tma_store;                     // 16-bit output: stage tiles in shared memory, store them by TMA
   int32_t nacc, nacc_log2, acc_cols;     // TMEM accumulator ring: 2 or 4 tiles, acc_cols columns apart
+  int32_t epi_alt;                       // epilogue groups of four warps take alternate tiles (BN = 64, staged stores)
   uint32_t *err;
   TcEpilogue epi;
 };
@@ -91,9 +92,17 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
                                                     uint32_t tempty0, int warp, int lane) {
   const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
   const int q = warp & 3;
-  uint32_t lt = 0;
+  const int set = (warp - 2) >> 2; // 0 or 1: which group of four warps this one belongs to
+  // 64-channel tiles with staged stores: the two groups take alternate tiles, each warp all 64 columns
+  // of its 32 rows (the per-tile chain of wait, TMEM load, conversion, staging writes, barriers and
+  // store is latency, not throughput: two chains in flight halve its cost per tile). Otherwise both
+  // groups work on every tile and split its columns in halves.
+  const bool alt = p.epi_alt != 0;
   bool ok = true;
-  for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++lt) {
+  for (uint32_t lt = alt ? (uint32_t)set : 0u; ok; lt += alt ? 2u : 1u) {
+    const int64_t tile64 = (int64_t)blockIdx.x + (int64_t)lt * gridDim.x;
+    if (tile64 >= p.total_tiles) break;
+    const int tile = (int)tile64;
     const int tp = tile % tiles_pix, tno = tile / tiles_pix;
     const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
     const int acc = (int)(lt & (uint32_t)(p.nacc - 1));
@@ -110,8 +119,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
     const int no0 = tno * p.BN;
     const uint32_t taddr = tmem_base + acc * p.acc_cols + ((uint32_t)(q * 32) << 16);
     const int nchunks = p.BN / 32;
-    const int set = (warp - 2) >> 2; // which half of the tile's columns this warp drains
-    const int c_begin = set * (nchunks / 2), c_end = c_begin + nchunks / 2;
+    const int c_begin = alt ? 0 : set * (nchunks / 2), c_end = alt ? nchunks : c_begin + nchunks / 2;
     if (p.tma_store) {
       // Converted rows go to a 128-byte-swizzled staging box (128 rows x 64 channels) and leave by
       // ONE tiled TMA store per box: whole 128-byte lines, clipped at the tensor's edges by the TMA
@@ -123,11 +131,11 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
       // both "this tile is written" and "the other buffer has been read" (the issuing thread waits
       // for its previous store's read before it arrives). Otherwise the four warps of a column half
       // own one buffer and BN / 128 boxes per tile, with a barrier before and after the writes.
-      const bool whole = p.BN == 64;
+      const bool whole = p.BN == 64 && !alt;
       const int bar_id = whole ? 1 : 1 + set, bar_threads = whole ? 256 : 128;
       const bool issuer = lane == 0 && warp == (whole ? 2 : 2 + 4 * set);
       const uint32_t buf = staging + (whole ? (lt & 1u) : (uint32_t)set) * BOX_BYTES;
-      const int boxes = whole ? 1 : p.BN / 128;
+      const int boxes = whole || alt ? 1 : p.BN / 128;
       const bool bf = p.epi.out_dtype == FB_DT_BFLOAT16;
       // 32 accumulator columns of this thread's row -> fused chain -> 16-bit -> four 16-byte chunks of
       // the row's 128-byte line in the staging box (chunk index XOR row: the 128-byte swizzle)
@@ -182,7 +190,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
       }
       // Two chunks per box; the TMEM load of the next chunk is in flight while this one is converted.
       for (int bx = 0; bx < boxes; ++bx) {
-        const int box_col0 = (set * boxes + bx) * 64; // first channel of the box within the tile
+        const int box_col0 = ((alt ? 0 : set * boxes) + bx) * 64; // first channel of the box within the tile
         const int c0 = c_begin + bx * 2;
         tmem_ld_wait();
         tmem_ld_32x32(taddr + (c0 + 1) * 32, raw_b);
@@ -253,7 +261,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), 8);
+      mbar_init(tempty_bar(a), p.epi_alt ? 4 : 8);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -399,7 +407,7 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
     for (int a = 0; a < 4; ++a) {
       mbar_init(tfull0 + 8u * a, 1);
-      mbar_init(tempty0 + 8u * a, 8);
+      mbar_init(tempty0 + 8u * a, p.epi_alt ? 4 : 8);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -742,6 +750,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
   // 16-bit outputs leave through staged TMA stores; the staging tiles come out of the ring's space
   p.tma_store = is16(out.dtype) ? 1 : 0;
   p.nacc = 2; p.nacc_log2 = 1; p.acc_cols = MAX_BN;
+  p.epi_alt = (p.tma_store && p.BN == 64) ? 1 : 0;
   const int ring_bytes = p.tma_store ? RING_BYTES_STAGED : RING_BYTES;
   bool halo = false;
   if (!v.pointwise_1x1 && v.R * v.S > 1 && v.dil_h == 1 && v.dil_w == 1 && v.R <= 7 && v.S <= 7) {

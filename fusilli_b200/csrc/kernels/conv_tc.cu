@@ -99,24 +99,38 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
   // groups work on every tile and split its columns in halves.
   const bool alt = p.epi_alt != 0;
   bool ok = true;
-  for (uint32_t lt = alt ? (uint32_t)set : 0u; ok; lt += alt ? 2u : 1u) {
-    const int64_t tile64 = (int64_t)blockIdx.x + (int64_t)lt * gridDim.x;
-    if (tile64 >= p.total_tiles) break;
-    const int tile = (int)tile64;
-    const int tp = tile % tiles_pix, tno = tile / tiles_pix;
-    const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
+  // This thread's pixel within a tile, and the tile coordinates as mixed-radix digits (w, h, image
+  // block, channel tile) that advance by the grid stride with carries: no division inside the loop.
+  const int row = q * 32 + lane;
+  const int dw = row % p.bw, dh = (row / p.bw) % p.bh, dn = row / (p.bw * p.bh);
+  const int64_t row_off0 = (int64_t)dn * p.out_sn + (int64_t)dh * p.out_sh + (int64_t)dw * p.out_sw;
+  const uint32_t lt0 = alt ? (uint32_t)set : 0u, lt_step = alt ? 2u : 1u;
+  int64_t tile = (int64_t)blockIdx.x + (int64_t)lt0 * gridDim.x;
+  const int64_t tile_step = (int64_t)lt_step * gridDim.x;
+  int tw, th, tb, tno, sw, sh, sb, sno;
+  {
+    const int64_t tp = tile % tiles_pix, sp = tile_step % tiles_pix;
+    tno = (int)(tile / tiles_pix); sno = (int)(tile_step / tiles_pix);
+    tw = (int)(tp % p.tiles_w); th = (int)((tp / p.tiles_w) % p.tiles_h); tb = (int)(tp / (p.tiles_w * p.tiles_h));
+    sw = (int)(sp % p.tiles_w); sh = (int)((sp / p.tiles_w) % p.tiles_h); sb = (int)(sp / (p.tiles_w * p.tiles_h));
+  }
+  for (uint32_t lt = lt0; ok && tile < p.total_tiles; lt += lt_step, tile += tile_step) {
     const int acc = (int)(lt & (uint32_t)(p.nacc - 1));
     const uint32_t aph = (lt >> p.nacc_log2) & 1;
+    const int w = tw * p.bw + dw, h = th * p.bh + dh, n = tb * p.bn + dn;
+    const bool row_ok = row < p.rows && w < p.W && h < p.H && n < p.N;
+    const int64_t row_off = row_off0 + (int64_t)(tb * p.bn) * p.out_sn + (int64_t)(th * p.bh) * p.out_sh +
+                            (int64_t)(tw * p.bw) * p.out_sw;
+    const int tw_c = tw, th_c = th, tb_c = tb, tno_c = tno; // this tile's digits; advance for the next one
+    tw += sw; if (tw >= p.tiles_w) { tw -= p.tiles_w; ++th; }
+    th += sh; if (th >= p.tiles_h) { th -= p.tiles_h; ++tb; }
+    tb += sb; if (tb >= p.tiles_nb) { tb -= p.tiles_nb; ++tno; }
+    tno += sno;
     TR_BEGIN;
     if (!mbar_wait(tfull0 + 8u * acc, aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     if (warp == 2) TR_ADD(5); // epilogue: waiting for a finished accumulator
     tc_fence_after();
-    const int row = q * 32 + lane;
-    const int dw = row % p.bw, dh = (row / p.bw) % p.bh, dn = row / (p.bw * p.bh);
-    const int w = tw * p.bw + dw, h = th * p.bh + dh, n = tb * p.bn + dn;
-    const bool row_ok = row < p.rows && w < p.W && h < p.H && n < p.N;
-    const int64_t row_off = (int64_t)n * p.out_sn + (int64_t)h * p.out_sh + (int64_t)w * p.out_sw;
-    const int no0 = tno * p.BN;
+    const int no0 = tno_c * p.BN;
     const uint32_t taddr = tmem_base + acc * p.acc_cols + ((uint32_t)(q * 32) << 16);
     const int nchunks = p.BN / 32;
     const int c_begin = alt ? 0 : set * (nchunks / 2), c_end = alt ? nchunks : c_begin + nchunks / 2;
@@ -183,7 +197,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
         named_barrier_sync(bar_id, bar_threads);
         if (warp == 2) TR_ADD(9);
         if (issuer) {
-          tma_store_4d(tmap_c, buf, no0, tw * p.bw, th * p.bh, tb * p.bn);
+          tma_store_4d(tmap_c, buf, no0, tw_c * p.bw, th_c * p.bh, tb_c * p.bn);
           tma_store_commit();
         }
         continue;
@@ -207,7 +221,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
         named_barrier_sync(bar_id, bar_threads);
         if (warp == 2) TR_ADD(9); // epilogue: barrier
         if (issuer) {
-          tma_store_4d(tmap_c, buf, no0 + box_col0, tw * p.bw, th * p.bh, tb * p.bn);
+          tma_store_4d(tmap_c, buf, no0 + box_col0, tw_c * p.bw, th_c * p.bh, tb_c * p.bn);
           tma_store_commit();
         }
       }

@@ -43,7 +43,7 @@ constexpr int A_BYTES = BM * BK * 2;
 constexpr int MAX_STAGES = 3, MAX_ACC = 8;
 constexpr int RING_BYTES = 221184; // 3 x 72 KB (BN = 64) or 2 x 96 KB (BN = 128) fit
 constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
-constexpr int NUM_THREADS = 352; // TMA warp, MMA warp, 8 epilogue warps, second TMA warp
+constexpr int NUM_THREADS = 384; // TMA warp, MMA warp, 8 epilogue warps, second TMA warp, second MMA warp
 constexpr int TMEM_COLS = 512;
 constexpr int PAIRS = 6;
 
@@ -169,38 +169,50 @@ conv_split_f32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 11) {
+    // Two warps issue alternate chunks (each chunk has its own accumulator and ring stages): the tensor
+    // pipe queues only a few instructions and a 128 x 64 x 16 MMA lasts 48 clk, so with one issuer the
+    // pipe ran dry during the barrier waits between two chunks.
+    const uint32_t which = warp == 1 ? 0u : 1u;
     const uint32_t idesc = make_idesc_f16(BM, p.BN, /*bf16*/ 1, 0, 0);
     const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
     const uint64_t b_desc0 = make_smem_desc(smem_base + 3 * A_BYTES, 16, 1024);
-    uint32_t ph = 0;
+    uint32_t ph = 0, g = 0; // g: chunks so far in this CTA
     int s = 0, acc = 0; // accumulator ring position and its phase
     uint32_t aph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-      for (int ch = 0; ch < p.nchunks && ok; ++ch) {
-        if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
-        for (int j = 0; j < p.chunk_steps; ++j, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
-          if (!mbar_wait_warp(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint64_t soff = (uint64_t)(((uint32_t)s * STAGE_BYTES) >> 4);
-#pragma unroll
-          for (int pr = 0; pr < PAIRS; ++pr) {
-            // X piece / W piece of product `pr`, smallest products first: (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
-            const int pa = pr == 1 ? 2 : ((pr == 2 || pr == 4) ? 1 : 0);
-            const int pb = pr == 0 ? 2 : ((pr == 2 || pr == 3) ? 1 : 0);
-            const uint64_t ad = a_desc0 + soff + (uint64_t)((uint32_t)(pa * A_BYTES) >> 4);
-            const uint64_t bd = b_desc0 + soff + (uint64_t)(((uint32_t)pb * p.b_bytes) >> 4);
-#pragma unroll
-            for (int k = 0; k < BK / 16; ++k)
-              tc_mma_f16_elect(d_tmem, ad + (uint64_t)((k * 32) >> 4), bd + (uint64_t)((k * 32) >> 4), idesc,
-                               (j > 0 || pr > 0 || k > 0) ? 1u : 0u);
+      for (int ch = 0; ch < p.nchunks && ok; ++ch, ++g) {
+        if ((g & 1u) != which) {
+          // the other warp's chunk: step over its stages
+          for (int j = 0; j < p.chunk_steps; ++j) {
+            s = (s + 1 == STAGES) ? 0 : s + 1;
+            ph ^= (s == 0);
           }
-          tc_commit_elect(empty_bar(s));
+        } else {
+          if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * p.BN);
+          for (int j = 0; j < p.chunk_steps; ++j, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+            if (!mbar_wait_warp(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t soff = (uint64_t)(((uint32_t)s * STAGE_BYTES) >> 4);
+#pragma unroll
+            for (int pr = 0; pr < PAIRS; ++pr) {
+              // X piece / W piece of product `pr`, smallest products first: (0,2) (2,0) (1,1) (0,1) (1,0) (0,0)
+              const int pa = pr == 1 ? 2 : ((pr == 2 || pr == 4) ? 1 : 0);
+              const int pb = pr == 0 ? 2 : ((pr == 2 || pr == 3) ? 1 : 0);
+              const uint64_t ad = a_desc0 + soff + (uint64_t)((uint32_t)(pa * A_BYTES) >> 4);
+              const uint64_t bd = b_desc0 + soff + (uint64_t)(((uint32_t)pb * p.b_bytes) >> 4);
+#pragma unroll
+              for (int k = 0; k < BK / 16; ++k)
+                tc_mma_f16_elect(d_tmem, ad + (uint64_t)((k * 32) >> 4), bd + (uint64_t)((k * 32) >> 4), idesc,
+                                 (j > 0 || pr > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit_elect(empty_bar(s));
+          }
+          if (ok) tc_commit_elect(tfull_bar(acc));
         }
-        if (ok) tc_commit_elect(tfull_bar(acc));
         acc = (acc + 1 == p.nacc) ? 0 : acc + 1;
         aph ^= (acc == 0);
       }

@@ -521,15 +521,21 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (ok && p.b_resident) ok = mbar_wait_warp(b_full(0), 0, p.err, ERR_WAIT_FULL);
     int sbs = 0;
     uint32_t phb = 0;
+    // patch slot and phase of this warp's first tile (channel blocks are numbered through the tiles)
+    int sa_next = (int)((first * (uint32_t)p.cblocks) % (uint32_t)p.a_slots);
+    uint32_t pha_next = ((first * (uint32_t)p.cblocks) / (uint32_t)p.a_slots) & 1u;
     for (uint32_t lt = first; ok; lt += step) {
       const int64_t tile = (int64_t)blockIdx.x + (int64_t)lt * gridDim.x;
       if (tile >= p.total_tiles) break;
       const int acc = (int)(lt & (uint32_t)(p.nacc - 1));
       const uint32_t aph = (lt >> p.nacc_log2) & 1;
-      // patch slot and phase of this tile's first channel block (blocks are numbered through the tiles)
-      const uint32_t blk0 = lt * (uint32_t)p.cblocks;
-      int sa = (int)(blk0 % (uint32_t)p.a_slots);
-      uint32_t pha = (blk0 / (uint32_t)p.a_slots) & 1u;
+      int sa = sa_next;
+      uint32_t pha = pha_next;
+      // the slot of this warp's next tile: `step` tiles of cblocks blocks further round the ring
+      for (uint32_t adv = step * (uint32_t)p.cblocks; adv > 0; --adv) {
+        sa_next = (sa_next + 1 == p.a_slots) ? 0 : sa_next + 1;
+        pha_next ^= (sa_next == 0);
+      }
       TR_BEGIN;
       if (!mbar_wait_warp(tempty0 + 8u * acc, aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
       TR_ADD(2); // MMA warp: waiting for a drained accumulator

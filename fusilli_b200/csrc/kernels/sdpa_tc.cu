@@ -1,8 +1,15 @@
 // Flash-style scaled-dot-product attention forward on the tensor cores:
 //   O = softmax(Q K^T * scale [causal]) V,  Q/K/V/O contiguous [B,H,S,128], bf16 or f16.
 //
-// One CTA per (256-query block, batch*head): two 128-query tiles that take turns on the tensor
-// pipe, so the softmax of one tile runs under the MMAs of the other. Memory stays O(S): K/V
+// Persistent CTAs, one per SM, each working through (256-query block, batch*head) items: two
+// 128-query tiles that take turns on the tensor pipe, so the softmax of one tile runs under the MMAs
+// of the other. Under a causal mask a CTA takes the query blocks of a head in pairs, the k-th heaviest
+// and then the k-th lightest, so every pair costs the same and a static round-robin over the pairs is
+// balanced; neighbouring CTAs work on the same head at the same time and share its K/V in L2. Barrier
+// phases run on across items, the next item's Q is loaded as soon as the last Q K^T of the current
+// one has read it and its first scores are computed while the softmax warps still drain the previous
+// output accumulator: TMEM allocation, barrier set-up and the first load latency are paid once per SM
+// instead of once per item. Memory stays O(S): K/V
 // stream through 2-stage shared-memory rings; scores, probabilities and the output accumulator
 // live in TMEM (512 columns: S0 | S1 | O0 | O1, 128 fp32 columns each).
 //   warp 0      TMA producer: both Q tiles once, then K_j / V_j tiles (128 keys x 128 dims, two
@@ -17,7 +24,7 @@
 //               running maximum has grown by more than 2^8 since the last rescale (decided per
 //               warp), so on most blocks the accumulator is never touched by the softmax warps.
 // Causal blocks above the diagonal are never loaded or multiplied; the diagonal block and a
-// ragged last key block are masked elementwise. Heavy (late) query blocks are scheduled first.
+// ragged last key block are masked elementwise.
 // Every mbarrier wait is bounded.
 #include <algorithm>
 
@@ -46,6 +53,7 @@ struct SdpaTcParams {
   int32_t B, Hq, Hk, Sq, Skv;
   int32_t causal, ab_format, out_dtype;
   int32_t q_blocks;
+  int32_t pairs_per_head, total_pairs;   // work units: (head, k) -> query blocks q_blocks-1-k and k
   float scale_log2e;
   void *out;
   uint32_t *err;
@@ -130,23 +138,39 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   // P_t is published in two halves (keys 0..63, 64..127) so that P V starts under the second half's exp
   auto p_half = [&](int t, int hf) { return bar_base + 8u * (11 + 2 * t + hf); };
   auto pv_done = [&](int t) { return bar_base + 8u * (15 + t); };
-  const uint32_t tmem_slot = bar_base + 8u * 17;
+  const uint32_t q_free = bar_base + 8u * 17;                              // Q tiles read by the item's last Q K^T
+  auto o_free = [&](int t) { return bar_base + 8u * (18 + t); };          // O_t drained by the softmax warps
+  const uint32_t tmem_slot = bar_base + 8u * 20;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // heavy query blocks (late rows under a causal mask) first
-  const int qb = p.q_blocks - 1 - (int)blockIdx.x;
-  const int bh = blockIdx.y;
-  const int b = bh / p.Hq, h = bh % p.Hq;
-  const int kvh = b * p.Hk + h / (p.Hq / p.Hk);
-  const int q0 = qb * (BQ * QTILES);
   const int nblk_all = (p.Skv + BKV - 1) / BKV;
-  // key blocks each tile needs; a tile that starts beyond Sq does nothing
-  auto blocks_of = [&](int t) {
-    const int qt = q0 + t * BQ;
-    return qt >= p.Sq ? 0 : (p.causal ? min(nblk_all, (qt + BQ - 1) / BKV + 1) : nblk_all);
+  // Item n of this CTA: pair u = blockIdx.x + (n / 2) * gridDim.x is (head u / pairs_per_head, k = u %
+  // pairs_per_head); its first half is query block q_blocks-1-k, its second half block k (no second
+  // half when both are the same block).
+  struct Item { bool any, valid; int bh, kvh, q0, nt0, nt1, nmax; };
+  auto item_of = [&](int n) {
+    Item it;
+    const int64_t u = (int64_t)blockIdx.x + (int64_t)(n >> 1) * gridDim.x;
+    it.any = u < p.total_pairs;
+    it.valid = false; it.bh = it.kvh = it.q0 = it.nt0 = it.nt1 = it.nmax = 0;
+    if (!it.any) return it;
+    const int bh = (int)(u / p.pairs_per_head), k = (int)(u % p.pairs_per_head);
+    const int qb = (n & 1) ? k : p.q_blocks - 1 - k;
+    if ((n & 1) && k == p.q_blocks - 1 - k) return it; // the middle block of an odd count: first half only
+    it.valid = true;
+    it.bh = bh;
+    const int b = bh / p.Hq, h = bh % p.Hq;
+    it.kvh = b * p.Hk + h / (p.Hq / p.Hk);
+    it.q0 = qb * (BQ * QTILES);
+    // key blocks each tile needs; a tile that starts beyond Sq does nothing
+    auto blocks_of = [&](int t) {
+      const int qt = it.q0 + t * BQ;
+      return qt >= p.Sq ? 0 : (p.causal ? min(nblk_all, (qt + BQ - 1) / BKV + 1) : nblk_all);
+    };
+    it.nt0 = blocks_of(0); it.nt1 = blocks_of(1);
+    it.nmax = max(it.nt0, it.nt1);
+    return it;
   };
-  const int nt[QTILES] = {blocks_of(0), blocks_of(1)};
-  const int nmax = max(nt[0], nt[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -159,7 +183,9 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(p_half(s, 0), 4);
       mbar_init(p_half(s, 1), 4);
       mbar_init(pv_done(s), 1);
+      mbar_init(o_free(s), 4);
     }
+    mbar_init(q_free, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -177,26 +203,36 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, QTILES * TILE_BYTES);
-#pragma unroll
-      for (int t = 0; t < QTILES; ++t) {
-        tma_load_3d(smem_base + SM_Q + t * TILE_BYTES, &tmap_q, q_full, 0, q0 + t * BQ, bh);
-        tma_load_3d(smem_base + SM_Q + t * TILE_BYTES + HALF_BYTES, &tmap_q, q_full, 64, q0 + t * BQ, bh);
-      }
       bool ok = true;
-      for (int j = 0; j < nmax && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(k_empty(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        mbar_expect_tx(k_full(s), TILE_BYTES);
-        const uint32_t sk = smem_base + SM_K + s * TILE_BYTES;
-        tma_load_3d(sk, &tmap_k, k_full(s), 0, j * BKV, kvh);
-        tma_load_3d(sk + HALF_BYTES, &tmap_k, k_full(s), 64, j * BKV, kvh);
-        if (!mbar_wait(v_empty(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        mbar_expect_tx(v_full(s), TILE_BYTES);
-        const uint32_t sv = smem_base + SM_V + s * TILE_BYTES;
-        tma_load_3d(sv, &tmap_v, v_full(s), 0, j * BKV, kvh);
-        tma_load_3d(sv + HALF_BYTES, &tmap_v, v_full(s), 64, j * BKV, kvh);
+      uint32_t g = 0;     // key blocks loaded so far: ring stage g & 1, phase (g >> 1) & 1
+      uint32_t items = 0; // valid items so far: phase of q_full / q_free
+      for (int n = 0; ok; ++n) {
+        const Item it = item_of(n);
+        if (!it.any) break;
+        if (!it.valid) continue;
+        // the previous item's last Q K^T has read the Q tiles
+        if (!mbar_wait(q_free, (items & 1) ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        mbar_expect_tx(q_full, QTILES * TILE_BYTES);
+#pragma unroll
+        for (int t = 0; t < QTILES; ++t) {
+          tma_load_3d(smem_base + SM_Q + t * TILE_BYTES, &tmap_q, q_full, 0, it.q0 + t * BQ, it.bh);
+          tma_load_3d(smem_base + SM_Q + t * TILE_BYTES + HALF_BYTES, &tmap_q, q_full, 64, it.q0 + t * BQ, it.bh);
+        }
+        ++items;
+        for (int j = 0; j < it.nmax && ok; ++j, ++g) {
+          const int s = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          if (!mbar_wait(k_empty(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(k_full(s), TILE_BYTES);
+          const uint32_t sk = smem_base + SM_K + s * TILE_BYTES;
+          tma_load_3d(sk, &tmap_k, k_full(s), 0, j * BKV, it.kvh);
+          tma_load_3d(sk + HALF_BYTES, &tmap_k, k_full(s), 64, j * BKV, it.kvh);
+          if (!mbar_wait(v_empty(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx(v_full(s), TILE_BYTES);
+          const uint32_t sv = smem_base + SM_V + s * TILE_BYTES;
+          tma_load_3d(sv, &tmap_v, v_full(s), 0, j * BKV, it.kvh);
+          tma_load_3d(sv + HALF_BYTES, &tmap_v, v_full(s), 64, j * BKV, it.kvh);
+        }
       }
     }
   } else if (warp == 1) {
@@ -213,9 +249,9 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint64_t q_desc0 = make_smem_desc(smem_base + SM_Q, 16, 1024);
     const uint64_t k_desc0 = make_smem_desc(smem_base + SM_K, 16, 1024);
     const uint64_t v_desc0 = make_smem_desc(smem_base + SM_V, HALF_BYTES, 1024);
-    auto issue_qk = [&](int t, int j) {
+    auto issue_qk = [&](int t, uint32_t stage) {
       const uint64_t qd = q_desc0 + (uint64_t)((t * TILE_BYTES) >> 4);
-      const uint64_t kd = k_desc0 + (uint64_t)(((j & 1) * TILE_BYTES) >> 4);
+      const uint64_t kd = k_desc0 + (uint64_t)((stage * TILE_BYTES) >> 4);
       if (leader) {
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -225,8 +261,8 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tc_commit(s_full(t));
       }
     };
-    auto issue_pv = [&](int t, int j, int hf) {
-      const uint64_t vd = v_desc0 + (uint64_t)(((j & 1) * TILE_BYTES) >> 4);
+    auto issue_pv = [&](int t, uint32_t stage, int j, int hf) {
+      const uint64_t vd = v_desc0 + (uint64_t)((stage * TILE_BYTES) >> 4);
       if (leader) {
 #pragma unroll
         for (int kk = 0; kk < BKV / 32; ++kk) {
@@ -237,158 +273,192 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (hf == 1) tc_commit(pv_done(t));
       }
     };
-    bool ok = mbar_wait(q_full, 0, p.err, ERR_WAIT_FULL);
-    if (ok && nmax > 0) {
-      ok = mbar_wait(k_full(0), 0, p.err, ERR_WAIT_FULL);
-      if (ok) {
+    bool ok = true;
+    uint32_t g = 0, items = 0;        // key blocks / valid items so far
+    uint32_t blk[QTILES] = {0, 0};    // key blocks of tile t so far: phase of s_full / p_half / pv_done
+    uint32_t drained[QTILES] = {0, 0}; // items of tile t so far: phase of o_free
+    for (int n = 0; ok; ++n) {
+      const Item it = item_of(n);
+      if (!it.any) break;
+      if (!it.valid) continue;
+      const int nt[QTILES] = {it.nt0, it.nt1};
+      if (!mbar_wait(q_full, items & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+      ++items;
+      if (it.nmax > 0) {
+        if (!mbar_wait(k_full(g & 1), (g >> 1) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int t = 0; t < QTILES; ++t)
-          if (nt[t] > 0) issue_qk(t, 0);
-        if (leader) tc_commit(k_empty(0));
-      }
-    }
-    for (int j = 0; j < nmax && ok; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(v_full(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-      if (j + 1 < nmax && !mbar_wait(k_full(s ^ 1), ((j + 1) >> 1) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-#pragma unroll
-      for (int t = 0; t < QTILES; ++t) {
-        if (j < nt[t]) {
-          if (!mbar_wait(p_half(t, 0), j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(t, j, 0);
-          if (!mbar_wait(p_half(t, 1), j & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
-          tc_fence_after();
-          issue_pv(t, j, 1);
+          if (nt[t] > 0) issue_qk(t, g & 1);
+        if (leader) {
+          tc_commit(k_empty(g & 1));
+          if (it.nmax == 1) tc_commit(q_free); // the only Q K^T of the item
         }
-        if (j + 1 < nt[t]) issue_qk(t, j + 1);
+      } else if (leader) {
+        tc_commit(q_free);
       }
-      if (!ok) break;
-      if (leader) {
-        tc_commit(v_empty(s));
-        if (j + 1 < nmax) tc_commit(k_empty(s ^ 1));
+      for (int j = 0; j < it.nmax && ok; ++j, ++g) {
+        const uint32_t s = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        if (!mbar_wait(v_full(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        if (j + 1 < it.nmax && !mbar_wait(k_full(s ^ 1), ((g + 1) >> 1) & 1, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+#pragma unroll
+        for (int t = 0; t < QTILES; ++t) {
+          if (j < nt[t]) {
+            // the item's first P V overwrites O_t: the previous item's output has been drained
+            if (j == 0 && !mbar_wait(o_free(t), (drained[t] & 1) ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+            if (!mbar_wait(p_half(t, 0), blk[t] & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, s, j, 0);
+            if (!mbar_wait(p_half(t, 1), blk[t] & 1, p.err, ERR_WAIT_OTHER)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, s, j, 1);
+            ++blk[t];
+          }
+          if (j + 1 < nt[t]) issue_qk(t, s ^ 1);
+        }
+        if (!ok) break;
+        if (leader) {
+          tc_commit(v_empty(s));
+          if (j + 1 < it.nmax) tc_commit(k_empty(s ^ 1));
+          if (j + 2 == it.nmax) tc_commit(q_free); // the item's last Q K^T is among the MMAs issued so far
+        }
       }
+#pragma unroll
+      for (int t = 0; t < QTILES; ++t)
+        if (nt[t] > 0) ++drained[t];
     }
   } else {
     const int t = (warp - 2) >> 2;     // query tile of this warp
     const int q = warp & 3;            // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;
-    const int q0t = q0 + t * BQ;
-    const int qi = q0t + row;
-    const int n_blocks = t ? nt[1] : nt[0];
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t s_addr = tmem_base + TM_S + t * BKV + lane_addr;
     const uint32_t o_addr = tmem_base + TM_O + t * HD + lane_addr;
     const float c = p.scale_log2e;
-    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      if (!mbar_wait(s_full(t), j & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-      const int k0 = j * BKV;
-      const bool need_mask = (k0 + BKV > p.Skv) || (p.causal && k0 + BKV - 1 > q0t);
-      const int k_lim = p.causal ? min(p.Skv, qi + 1) : p.Skv; // keys >= k_lim are masked for this row
-      // the whole score row of this block, one pass
-      uint32_t raw[BKV];
-#pragma unroll
-      for (int cc = 0; cc < BKV / 32; ++cc) tmem_ld_32x32(s_addr + cc * 32, raw + cc * 32);
-      tmem_ld_wait();
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < BKV; ++i)
-          if (k0 + i >= k_lim) raw[i] = 0xff800000u; // -inf
+    uint32_t blk = 0; // key blocks of this tile so far: phase of s_full / pv_done
+    for (int n = 0; ok; ++n) {
+      const Item it = item_of(n);
+      if (!it.any) break;
+      if (!it.valid) continue;
+      const int bh = it.bh;
+      const int q0t = it.q0 + t * BQ;
+      const int qi = q0t + row;
+      const int n_blocks = t ? it.nt1 : it.nt0;
+      float m_ref = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n_blocks && ok; ++j, ++blk) {
+        if (!mbar_wait(s_full(t), blk & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const int k0 = j * BKV;
+        const bool need_mask = (k0 + BKV > p.Skv) || (p.causal && k0 + BKV - 1 > q0t);
+        const int k_lim = p.causal ? min(p.Skv, qi + 1) : p.Skv; // keys >= k_lim are masked for this row
+        // the whole score row of this block, one pass
+        uint32_t raw[BKV];
+  #pragma unroll
+        for (int cc = 0; cc < BKV / 32; ++cc) tmem_ld_32x32(s_addr + cc * 32, raw + cc * 32);
+        tmem_ld_wait();
+        if (need_mask) {
+  #pragma unroll
+          for (int i = 0; i < BKV; ++i)
+            if (k0 + i >= k_lim) raw[i] = 0xff800000u; // -inf
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+  #pragma unroll
+        for (int i = 0; i < BKV; i += 8) {
+          mx0 = max3(mx0, __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
+          mx1 = max3(mx1, __uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3]));
+          mx2 = max3(mx2, __uint_as_float(raw[i + 4]), __uint_as_float(raw[i + 5]));
+          mx3 = max3(mx3, __uint_as_float(raw[i + 6]), __uint_as_float(raw[i + 7]));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // Rescale only when some row of the warp moved its maximum by more than 2^RESCALE_LOG2
+        // (always on the first block): until then probabilities are taken against the stale
+        // maximum and stay below 2^RESCALE_LOG2, which fp32 sums and 16-bit P hold exactly as well.
+        const bool grow = mx > m_ref && ((mx - m_ref) * c > RESCALE_LOG2 || m_ref == -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = fmaxf(m_ref, mx);
+          const float m_use = (m_new == -INFINITY) ? 0.f : m_new; // a fully masked row so far
+          const float alpha = (m_ref == -INFINITY) ? 0.f : ex2_approx((m_ref - m_use) * c);
+          if (j > 0) {
+            if (!mbar_wait(pv_done(t), (blk - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+            tc_fence_after();
+  #pragma unroll 1
+            for (int cc = 0; cc < HD / 32; ++cc) {
+              uint32_t acc[32];
+              tmem_ld_32x32(o_addr + cc * 32, acc);
+              tmem_ld_wait();
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
+              tmem_st_32x32(o_addr + cc * 32, acc);
+            }
+          }
+          l_run *= alpha;
+          m_ref = (m_new == -INFINITY) ? -INFINITY : m_use;
+        }
+        const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
+        // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
+        // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
+        const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
+        float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
+  #pragma unroll
+        for (int cc = 0; cc < BKV / 32; ++cc) {
+          uint32_t packed[16];
+  #pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 x = f2_fma(make_float2(__uint_as_float(raw[cc * 32 + 2 * i]), __uint_as_float(raw[cc * 32 + 2 * i + 1])),
+                                    c2, nmc2);
+            float2 pr;
+            if ((i & SDPA_POLY_AND) == SDPA_POLY_EQ) {
+              pr = ex2_poly(x);
+            } else {
+              pr.x = ex2_approx(x.x);
+              pr.y = ex2_approx(x.y);
+            }
+            if (i & 1) lb = f2_add(lb, pr);
+            else la = f2_add(la, pr);
+            if (p.ab_format) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(pr.x, pr.y);
+              packed[i] = *reinterpret_cast<uint32_t *>(&hh);
+            } else {
+              __half2 hh = __floats2half2_rn(pr.x, pr.y);
+              packed[i] = *reinterpret_cast<uint32_t *>(&hh);
+            }
+          }
+          tmem_st_32x16(s_addr + cc * 16, packed);
+          if (cc & 1) {
+            // half of P (and, the first time, a rescaled accumulator) is in TMEM: let the MMA warp
+            // issue that half of P V
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_half(t, cc >> 1));
+          }
+        }
+        l_run += (la.x + la.y) + (lb.x + lb.y);
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < BKV; i += 8) {
-        mx0 = max3(mx0, __uint_as_float(raw[i]), __uint_as_float(raw[i + 1]));
-        mx1 = max3(mx1, __uint_as_float(raw[i + 2]), __uint_as_float(raw[i + 3]));
-        mx2 = max3(mx2, __uint_as_float(raw[i + 4]), __uint_as_float(raw[i + 5]));
-        mx3 = max3(mx3, __uint_as_float(raw[i + 6]), __uint_as_float(raw[i + 7]));
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // Rescale only when some row of the warp moved its maximum by more than 2^RESCALE_LOG2
-      // (always on the first block): until then probabilities are taken against the stale
-      // maximum and stay below 2^RESCALE_LOG2, which fp32 sums and 16-bit P hold exactly as well.
-      const bool grow = mx > m_ref && ((mx - m_ref) * c > RESCALE_LOG2 || m_ref == -INFINITY);
-      if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = fmaxf(m_ref, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new; // a fully masked row so far
-        const float alpha = (m_ref == -INFINITY) ? 0.f : ex2_approx((m_ref - m_use) * c);
-        if (j > 0) {
-          if (!mbar_wait(pv_done(t), (j - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      if (ok && n_blocks > 0) {
+        if (mbar_wait(pv_done(t), (blk - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) {
           tc_fence_after();
-#pragma unroll 1
+          const float inv = 1.f / l_run;
+          const int64_t row_off = ((int64_t)bh * p.Sq + qi) * HD;
+  #pragma unroll 1
           for (int cc = 0; cc < HD / 32; ++cc) {
             uint32_t acc[32];
             tmem_ld_32x32(o_addr + cc * 32, acc);
             tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = __float_as_uint(__uint_as_float(acc[i]) * alpha);
-            tmem_st_32x32(o_addr + cc * 32, acc);
+            float v[32];
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * inv;
+            if (qi < p.Sq) epi_store32(p.out, p.out_dtype, row_off + cc * 32, v, 32);
           }
-        }
-        l_run *= alpha;
-        m_ref = (m_new == -INFINITY) ? -INFINITY : m_use;
-      }
-      const float mc = (m_ref == -INFINITY) ? 0.f : m_ref * c;
-      // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
-      // probabilities -> 16-bit pairs -> TMEM (the A operand of P V), 32 keys at a time
-      const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
-      float2 la = make_float2(0.f, 0.f), lb = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int cc = 0; cc < BKV / 32; ++cc) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 x = f2_fma(make_float2(__uint_as_float(raw[cc * 32 + 2 * i]), __uint_as_float(raw[cc * 32 + 2 * i + 1])),
-                                  c2, nmc2);
-          float2 pr;
-          if ((i & SDPA_POLY_AND) == SDPA_POLY_EQ) {
-            pr = ex2_poly(x);
-          } else {
-            pr.x = ex2_approx(x.x);
-            pr.y = ex2_approx(x.y);
-          }
-          if (i & 1) lb = f2_add(lb, pr);
-          else la = f2_add(la, pr);
-          if (p.ab_format) {
-            __nv_bfloat162 hh = __floats2bfloat162_rn(pr.x, pr.y);
-            packed[i] = *reinterpret_cast<uint32_t *>(&hh);
-          } else {
-            __half2 hh = __floats2half2_rn(pr.x, pr.y);
-            packed[i] = *reinterpret_cast<uint32_t *>(&hh);
-          }
-        }
-        tmem_st_32x16(s_addr + cc * 16, packed);
-        if (cc & 1) {
-          // half of P (and, the first time, a rescaled accumulator) is in TMEM: let the MMA warp
-          // issue that half of P V
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(p_half(t, cc >> 1));
         }
       }
-      l_run += (la.x + la.y) + (lb.x + lb.y);
-    }
-    if (ok && n_blocks > 0) {
-      if (mbar_wait(pv_done(t), (n_blocks - 1) & 1, p.err, ERR_WAIT_TMEM_FULL)) {
-        tc_fence_after();
-        const float inv = 1.f / l_run;
-        const int64_t row_off = ((int64_t)bh * p.Sq + qi) * HD;
-#pragma unroll 1
-        for (int cc = 0; cc < HD / 32; ++cc) {
-          uint32_t acc[32];
-          tmem_ld_32x32(o_addr + cc * 32, acc);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]) * inv;
-          if (qi < p.Sq) epi_store32(p.out, p.out_dtype, row_off + cc * 32, v, 32);
-        }
+      // O_t may be overwritten by the next item's first P V
+      if (n_blocks > 0) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_free(t));
       }
     }
   }
@@ -465,7 +535,11 @@ fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s) {
   cudaError_t ae = set_max_dynamic_smem(reinterpret_cast<const void *>(sdpa_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("sdpa_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
-  dim3 grid((unsigned)p.q_blocks, (unsigned)(p.B * p.Hq));
+  p.pairs_per_head = (p.q_blocks + 1) / 2;
+  const int64_t pairs = (int64_t)p.pairs_per_head * p.B * p.Hq;
+  FB_REQUIRE(pairs < (1ll << 31), FB_NOT_IMPLEMENTED, "sdpa_tcgen05: too many query blocks");
+  p.total_pairs = (int)pairs;
+  const int grid = (int)std::min<int64_t>(pairs, cx.dev->sm_count);
   sdpa_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tq, tk, tv, p);
   return FB_OK;
 }

@@ -10,6 +10,11 @@
 // group; each tap accumulates into its own TMEM columns (taps x BN <= 512). On narrow layers
 // (BN <= 128) the shifted X boxes of up to 256 / BN taps land side by side in one B stage and are
 // one MMA operand, N = taps x BN, writing those taps' adjacent column ranges at once.
+// On 64-channel layers with R x S > 1 (unit dilation) the X operand comes from a haloed patch instead:
+// a CTA owns one filter COLUMN s, loads per 8 x 8 pixel patch ONE box of 8 x (8+R-1) input pixels
+// shifted by s, and the R taps of the column are the 64-channel blocks of a single B operand whose
+// blocks are 1024 bytes (one image row of the patch) apart: one MMA of N = 64 R per 16 pixels, 10 KB of
+// X per patch instead of R boxes of 8 KB.
 // The pixel reduction is split across CTAs: a CTA owns (ko tile, c tile, tap group, pixel
 // slice), writes its fp32 partial filter to the workspace, and a second kernel adds the
 // slices in a fixed order and converts -- deterministic, no atomics.
@@ -31,8 +36,10 @@ constexpr int HALF = 64 * KPIX * 2;              // one [64 pixels][64 channels]
 // of 8 KB on a 1x1 C64 layer against 3 + 4 stages of 16 / 32 KB on the wide ones.
 constexpr int A_RING_BYTES = 3 * BM * KPIX * 2, B_RING_BYTES = 4 * MAX_BN * KPIX * 2;
 constexpr int MAX_A_STAGES = 6, MAX_B_STAGES = 12;
-constexpr int SMEM_BYTES = A_RING_BYTES + B_RING_BYTES + 1024 + 512;
-constexpr int NUM_THREADS = 192;
+// With haloed X patches the two rings share 220 KB and are split per layer (p.a_ring_bytes).
+constexpr int HALO_RING_BYTES = 220 * 1024;
+constexpr int SMEM_BYTES = HALO_RING_BYTES + 1024 + 512;
+constexpr int NUM_THREADS = 224; // warps 0, 3, 4, 5: X producers; 1 (and 6 with haloed patches): MMA issue; 2: dY producer; 2..5 drain the accumulators
 constexpr int B_PRODUCERS = 4; // warps 0, 3, 4, 5 take every fourth B stage each
 constexpr int TMEM_COLS = 512;
 
@@ -45,7 +52,10 @@ struct WgradTcParams {
   int32_t patches_total, patches_per_slice, slices;
   int32_t k_tiles, c_tiles, ngroups, taps_per_group, BN, a_halves;
   int32_t tpack;            // filter taps that share one B stage and one MMA (tpack * BN <= 256)
+  int32_t halo;             // haloed X patches: the CTA's tap group is filter column `grp`, its taps the R rows
+  int32_t issuers;          // MMA-issuing warps (2 with haloed patches and R >= 2: they split the column's taps)
   int32_t a_stages, b_stages, a_stage_bytes, b_stage_bytes;
+  int32_t a_ring_bytes;     // bytes of the dY ring; the X ring follows
   float *partial;           // [slices][Kout][R*S][C] fp32
   uint32_t *err;
 };
@@ -57,8 +67,8 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int A_STAGES = p.a_stages, B_STAGES = p.b_stages;
   const uint32_t A_STAGE_BYTES = (uint32_t)p.a_stage_bytes, B_STAGE_BYTES = (uint32_t)p.b_stage_bytes;
-  const uint32_t sb_base = smem_base + A_RING_BYTES;
-  const uint32_t bar_base = sb_base + B_RING_BYTES;
+  const uint32_t sb_base = smem_base + (uint32_t)p.a_ring_bytes;
+  const uint32_t bar_base = smem_base + HALO_RING_BYTES;
   auto a_full = [&](int s) { return bar_base + 8u * s; };
   auto a_empty = [&](int s) { return bar_base + 8u * (MAX_A_STAGES + s); };
   auto b_full = [&](int s) { return bar_base + 8u * (2 * MAX_A_STAGES + s); };
@@ -73,16 +83,18 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   const int ct = u % p.c_tiles; u /= p.c_tiles;
   const int grp = u % p.ngroups;
   const int slice = u / p.ngroups;
-  const int tap0 = grp * p.taps_per_group;
-  const int ntaps = min(p.taps_per_group, p.R * p.S - tap0);
+  const int tap0 = p.halo ? 0 : grp * p.taps_per_group;
+  const int ntaps = p.halo ? p.R : min(p.taps_per_group, p.R * p.S - tap0);
   const int patch0 = slice * p.patches_per_slice;
   const int npatch = min(p.patches_per_slice, p.patches_total - patch0);
-  const uint32_t a_bytes = (uint32_t)p.a_halves * HALF, b_bytes = (uint32_t)p.BN * KPIX * 2;
+  const uint32_t img = p.halo ? (uint32_t)p.bn : 1u; // images per stage (haloed patches take two)
+  const uint32_t a_bytes = (uint32_t)p.a_halves * HALF * img, b_bytes = (uint32_t)p.BN * KPIX * 2;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < A_STAGES; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), 1); }
-    for (int s = 0; s < B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-    mbar_init(acc_full, 1);
+    // every issuing warp releases a stage and reports its accumulators
+    for (int s = 0; s < A_STAGES; ++s) { mbar_init(a_full(s), 1); mbar_init(a_empty(s), p.issuers); }
+    for (int s = 0; s < B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), p.issuers); }
+    mbar_init(acc_full, p.issuers);
     fence_barrier_init();
     tma_prefetch_desc(&tmap_dy);
     tma_prefetch_desc(&tmap_x);
@@ -113,7 +125,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       mbar_expect_tx_elect(a_full(sa_i), a_bytes);
       const uint32_t sa = smem_base + (uint32_t)sa_i * A_STAGE_BYTES;
       for (int hh = 0; hh < p.a_halves; ++hh)
-        tma_load_4d_elect(sa + hh * HALF, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
+        tma_load_4d_elect(sa + hh * HALF * img, &tmap_dy, a_full(sa_i), kt * BM + 64 * hh, w0, h0, n0);
       sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
       pha ^= (sa_i == 0);
       if (++tw == p.tiles_w) {
@@ -129,6 +141,34 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
     int sb_i = 0, chunk = 0;
     uint32_t phb = 0;
     bool ok = true;
+    if (p.halo) {
+      // one stage per patch: the 8 x (bh+R-1) input pixels under the patch for filter column grp
+      // No more producer warps than stages: a warp's consecutive loads must be consecutive uses of their
+      // stage. (With four warps on three stages a warp's second load was the THIRD use of its stage, its
+      // parity wait passed on the barrier's initial phase, and the stage's full barrier got a second
+      // arrival in one phase: a launch failure.)
+      const int nprod = min(B_PRODUCERS, B_STAGES);
+      if (id >= nprod) return;
+      int tw = patch0 % p.tiles_w, th = (patch0 / p.tiles_w) % p.tiles_h, tb = patch0 / (p.tiles_w * p.tiles_h);
+      for (int pi = 0; pi < npatch && ok; ++pi) {
+        if (pi % nprod == id) {
+          if (!mbar_wait_warp(b_empty(sb_i), phb ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_expect_tx_elect(b_full(sb_i), B_STAGE_BYTES);
+          tma_load_4d_elect(sb_base + (uint32_t)sb_i * B_STAGE_BYTES, &tmap_x, b_full(sb_i), ct * p.BN,
+                            tw * p.bw - p.pad_w + grp, th * p.bh - p.pad_h, tb * p.bn);
+        }
+        sb_i = (sb_i + 1 == B_STAGES) ? 0 : sb_i + 1;
+        phb ^= (sb_i == 0);
+        if (++tw == p.tiles_w) {
+          tw = 0;
+          if (++th == p.tiles_h) {
+            th = 0;
+            ++tb;
+          }
+        }
+      }
+      return;
+    }
     const int ts0 = tap0 % p.S, tr0 = tap0 / p.S;
     int tw = patch0 % p.tiles_w, th = (patch0 / p.tiles_w) % p.tiles_h, tb = patch0 / (p.tiles_w * p.tiles_h);
     for (int pi = 0; pi < npatch && ok; ++pi) {
@@ -169,7 +209,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
 
   if (warp == 0) {
     produce_b(0);
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 6) {
     // The whole warp runs the loop (addresses and descriptors stay in uniform registers); one
     // elected lane issues the MMAs and the commits, which track the issuing thread.
     // one instruction descriptor per number of taps in a stage (N = taps * BN)
@@ -182,8 +222,42 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
     const uint64_t b_desc0 = make_smem_desc(sb_base, HALF, 1024);
     int sa_i = 0, sb_i = 0;
     uint32_t pha = 0, phb = 0;
-    bool ok = true;
-    for (int pi = 0; pi < npatch && ok; ++pi) {
+    bool ok = warp == 1 || p.issuers == 2, npatch_done = false;
+    if (p.halo && ok) {
+      // The taps of the column are ONE B operand: N = 64 x taps, the taps' 64-channel blocks one patch row
+      // (1024 B) apart. With two issuing warps the first takes the upper half of the rows and the second
+      // the rest, each into TMEM columns of its own (one issuing thread and a fixed order of sums per
+      // accumulator): four MMAs per patch are ~400 clk of tensor time between two barrier waits of ~200
+      // clk each, and the pipe queues only two or three instructions.
+      const int r_first = p.issuers == 2 ? (p.R + 1) / 2 : p.R;
+      const int r0 = warp == 1 ? 0 : r_first, nr = warp == 1 ? r_first : p.R - r_first;
+      const uint32_t idesc_h = make_idesc_f16(BM, nr * 64, p.ab_format, 1, 1);
+      const uint64_t bh_desc0 = make_smem_desc(sb_base + (uint32_t)r0 * 1024u, 1024, 1024);
+      const uint64_t ah_desc0 = make_smem_desc(smem_base, HALF * img, 1024); // 64-channel blocks of dY: img boxes apart
+      const uint32_t d_tmem = tmem_base + (uint32_t)(r0 * 64);
+      const uint32_t x_img = (uint32_t)(p.bh + p.R - 1) * 1024u; // one image's rows of the X box
+      const int ksteps = (KPIX / 16) * (int)img;
+      for (int pi = 0; pi < npatch && ok; ++pi) {
+        if (!mbar_wait_warp(a_full(sa_i), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        if (!mbar_wait_warp(b_full(sb_i), phb, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t ad = ah_desc0 + (uint64_t)(((uint32_t)sa_i * A_STAGE_BYTES) >> 4);
+        const uint64_t bd = bh_desc0 + (uint64_t)(((uint32_t)sb_i * B_STAGE_BYTES) >> 4);
+        for (int k = 0; k < ksteps; ++k) // 16 pixels = two patch rows per step; the images' X rows are x_img apart
+          tc_mma_f16_elect(d_tmem, ad + (uint64_t)((k * 2048) >> 4),
+                           bd + (uint64_t)(((uint32_t)(k >> 2) * x_img + (uint32_t)(k & 3) * 2048u) >> 4), idesc_h,
+                           (pi > 0 || k > 0) ? 1u : 0u);
+        tc_commit_elect(b_empty(sb_i));
+        tc_commit_elect(a_empty(sa_i));
+        sb_i = (sb_i + 1 == B_STAGES) ? 0 : sb_i + 1;
+        phb ^= (sb_i == 0);
+        sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
+        pha ^= (sa_i == 0);
+      }
+      npatch_done = true;
+    }
+    if (warp != 1) npatch_done = true;
+    for (int pi = 0; pi < npatch && ok && !npatch_done; ++pi) {
       if (!mbar_wait_warp(a_full(sa_i), pha, p.err, ERR_WAIT_FULL)) { ok = false; break; }
       const uint64_t ad = a_desc0 + (uint64_t)(((uint32_t)sa_i * A_STAGE_BYTES) >> 4);
       for (int t = 0; t < ntaps; t += p.tpack) {
@@ -204,7 +278,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
       sa_i = (sa_i + 1 == A_STAGES) ? 0 : sa_i + 1;
       pha ^= (sa_i == 0);
     }
-    if (ok) tc_commit_elect(acc_full);
+    if (ok && (warp == 1 || p.issuers == 2)) tc_commit_elect(acc_full);
   } else {
     if (warp == 2) produce_a();
     if (warp >= 3) produce_b(warp - 2);
@@ -228,7 +302,8 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
         }
         const int c0 = ct * p.BN + cc * 32;
         if (ko < p.Kout && c0 < p.C) {
-          float *dst = p.partial + (((int64_t)slice * p.Kout + ko) * taps_all + (tap0 + t)) * p.C + c0;
+          const int tap = p.halo ? t * p.S + grp : tap0 + t; // halo: row t of filter column grp
+          float *dst = p.partial + (((int64_t)slice * p.Kout + ko) * taps_all + tap) * p.C + c0;
           if (c0 + 32 <= p.C && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -334,7 +409,17 @@ bool wgrad_view(const Plan &p, const Step &s, WgradView &v) {
 struct WgradTiling {
   int bw, bh, bn, tiles_w, tiles_h, tiles_nb, patches;
   int k_tiles, c_tiles, BN, ngroups, taps_per_group, slices, per_slice;
+  int halo;
 };
+
+// FUSILLI_B200_WGRAD_HALO=0 at plan build AND execute keeps the per-tap X boxes.
+bool wgrad_halo_off() {
+  static const bool off = [] {
+    const char *e = getenv("FUSILLI_B200_WGRAD_HALO");
+    return e && e[0] == '0';
+  }();
+  return off;
+}
 
 void wgrad_tiling(const WgradView &v, WgradTiling &t) {
   // 64-pixel patches with power-of-two sides (the K block must be exactly 64 rows)
@@ -361,6 +446,29 @@ void wgrad_tiling(const WgradView &v, WgradTiling &t) {
   t.ngroups = (taps * t.BN + TMEM_COLS - 1) / TMEM_COLS;
   t.taps_per_group = (taps + t.ngroups - 1) / t.ngroups;
   t.ngroups = (taps + t.taps_per_group - 1) / t.taps_per_group;
+  // Haloed X patches (one CTA per filter column): 64-channel tiles, unit dilation, R taps = N <= 256, and
+  // an image that 8 x 8 patches tile without much waste
+  t.halo = 0;
+  if (taps > 1 && t.BN == 64 && v.dil_h == 1 && v.dil_w == 1 && v.R <= 4 && v.S <= 8 && !wgrad_halo_off()) {
+    const int64_t tiles = (int64_t)((v.Q + 7) / 8) * ((v.P + 7) / 8) * v.N;
+    if ((double)v.N * v.P * v.Q / ((double)tiles * 64.0) >= 0.75) {
+      t.halo = 1;
+      // Several images per stage: 4 MMAs per image between two barrier waits (~200 clk each even on a
+      // completed barrier; 120 -> 103 us on 56x56 C64 3x3 with two images). The most images that leave
+      // three stages of both rings.
+      const int a_halves = v.Kout > 64 ? 2 : 1;
+      t.bw = 8; t.bh = 8; t.bn = 1;
+      for (int n = 4; n > 1; n /= 2)
+        if (n <= v.N && 3 * n * (a_halves * HALF + (8 + v.R - 1) * 1024) <= HALO_RING_BYTES) {
+          t.bn = n;
+          break;
+        }
+      t.tiles_w = (v.Q + 7) / 8; t.tiles_h = (v.P + 7) / 8; t.tiles_nb = (v.N + t.bn - 1) / t.bn;
+      t.patches = t.tiles_w * t.tiles_h * t.tiles_nb;
+      t.ngroups = v.S;
+      t.taps_per_group = v.R;
+    }
+  }
   const int units = t.k_tiles * t.c_tiles * t.ngroups;
   // One CTA per SM: with two per SM (which run one after the other: shared memory and TMEM admit
   // one) every layer was 7-15 % slower, each CTA paying its own prologue, first-load latency and
@@ -418,10 +526,19 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
   p.BN = t.BN;
   p.a_halves = (v.Kout - 0 > 64) ? 2 : 1;
   p.tpack = std::max(1, std::min(4, MAX_BN / t.BN));
-  p.a_stage_bytes = p.a_halves * HALF;
-  p.b_stage_bytes = std::min(p.tpack, t.taps_per_group) * (t.BN / 64) * HALF;
-  p.a_stages = std::min(MAX_A_STAGES, A_RING_BYTES / p.a_stage_bytes);
-  p.b_stages = std::min(MAX_B_STAGES, B_RING_BYTES / p.b_stage_bytes);
+  p.halo = t.halo;
+  p.issuers = 1; // a second issuing warp on the column's lower taps was slower (140 against 120 us on 56x56 C64 3x3)
+  p.a_stage_bytes = p.a_halves * HALF * (t.halo ? t.bn : 1);
+  p.b_stage_bytes = t.halo ? t.bn * (t.bh + v.R - 1) * 1024 : std::min(p.tpack, t.taps_per_group) * (t.BN / 64) * HALF;
+  if (t.halo) {
+    const int st = std::min(MAX_A_STAGES, HALO_RING_BYTES / (p.a_stage_bytes + p.b_stage_bytes));
+    p.a_stages = p.b_stages = st;
+    p.a_ring_bytes = st * p.a_stage_bytes;
+  } else {
+    p.a_stages = std::min(MAX_A_STAGES, A_RING_BYTES / p.a_stage_bytes);
+    p.b_stages = std::min(MAX_B_STAGES, B_RING_BYTES / p.b_stage_bytes);
+    p.a_ring_bytes = A_RING_BYTES;
+  }
   p.partial = reinterpret_cast<float *>(cx.workspace + s.scratch_offset);
   p.err = cx.dev->error_word;
   CUtensorMap tmDy, tmX;
@@ -435,7 +552,7 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
   {
     uint64_t dims[4] = {(uint64_t)v.C, (uint64_t)v.XW, (uint64_t)v.XH, (uint64_t)v.N};
     uint64_t str[3] = {(uint64_t)v.C * 2, (uint64_t)v.XW * v.C * 2, (uint64_t)v.XH * v.XW * v.C * 2};
-    uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)t.bh, (uint32_t)t.bn};
+    uint32_t box[4] = {64, (uint32_t)t.bw, (uint32_t)(t.halo ? t.bh + v.R - 1 : t.bh), (uint32_t)t.bn};
     FB_REQUIRE(encode_tmap_2byte(&tmX, xp, 4, dims, str, box, &why), FB_RUNTIME_FAILURE, why);
   }
   cudaError_t ae =

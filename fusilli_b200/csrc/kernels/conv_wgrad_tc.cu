@@ -421,7 +421,15 @@ bool wgrad_halo_off() {
   return off;
 }
 
-void wgrad_tiling(const WgradView &v, WgradTiling &t) {
+int wgrad_halo_max_c() {
+  static const int c = [] {
+    const char *e = getenv("FUSILLI_B200_WGRAD_HALO_MAXC");
+    return e ? atoi(e) : 128;
+  }();
+  return c;
+}
+
+void wgrad_tiling(const WgradView &v, WgradTiling &t, bool allow_halo = true) {
   // 64-pixel patches with power-of-two sides (the K block must be exactly 64 rows)
   double best = -1.0;
   t.bw = 8; t.bh = 8; t.bn = 1;
@@ -449,10 +457,12 @@ void wgrad_tiling(const WgradView &v, WgradTiling &t) {
   // Haloed X patches (one CTA per filter column): 64-channel tiles, unit dilation, R taps = N <= 256, and
   // an image that 8 x 8 patches tile without much waste
   t.halo = 0;
-  if (taps > 1 && t.BN == 64 && v.dil_h == 1 && v.dil_w == 1 && v.R <= 4 && v.S <= 8 && !wgrad_halo_off()) {
+  if (allow_halo && taps > 1 && v.C <= wgrad_halo_max_c() && v.dil_h == 1 && v.dil_w == 1 && v.R <= 4 && v.S <= 8 && !wgrad_halo_off()) {
     const int64_t tiles = (int64_t)((v.Q + 7) / 8) * ((v.P + 7) / 8) * v.N;
     if ((double)v.N * v.P * v.Q / ((double)tiles * 64.0) >= 0.75) {
       t.halo = 1;
+      t.BN = 64; // a CTA takes 64 input channels of one filter column
+      t.c_tiles = (v.C + 63) / 64;
       // Several images per stage: 4 MMAs per image between two barrier waits (~200 clk each even on a
       // completed barrier; 120 -> 103 us on 56x56 C64 3x3 with two images). The most images that leave
       // three stages of both rings.
@@ -474,7 +484,9 @@ void wgrad_tiling(const WgradView &v, WgradTiling &t) {
   // one) every layer was 7-15 % slower, each CTA paying its own prologue, first-load latency and
   // accumulator drain, and the slice reduction reading twice the partials.
   int slices = std::max(1, 148 / units);
-  slices = std::min(slices, std::max(1, t.patches / 8));
+  // at least eight stages per slice; counted in image patches where a stage holds several images, so that
+  // the slice count (and the workspace) never shrinks when the batch grows
+  slices = std::min(slices, std::max(1, t.halo ? (t.tiles_w * t.tiles_h * v.N) / 32 : t.patches / 8));
   t.per_slice = (t.patches + slices - 1) / slices;
   t.slices = (t.patches + t.per_slice - 1) / t.per_slice;
 }
@@ -490,10 +502,13 @@ bool conv_wgrad_tc_eligible(const Plan &p, const Step &s) {
 int64_t conv_wgrad_tc_scratch_bytes(const Plan &p, const Step &s, int32_t *slices) {
   WgradView v;
   if (!wgrad_view(p, s, v)) return 0;
-  WgradTiling t;
+  WgradTiling t, plain;
   wgrad_tiling(v, t);
+  wgrad_tiling(v, plain, false);
   *slices = t.slices;
-  return (int64_t)t.slices * v.Kout * v.R * v.S * v.C * 4;
+  // A plan with dynamic dims is specialised per shape and a smaller shape may take the other tiling: the
+  // workspace of the representative shape covers both.
+  return (int64_t)std::max(t.slices, plain.slices) * v.Kout * v.R * v.S * v.C * 4;
 }
 
 fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {

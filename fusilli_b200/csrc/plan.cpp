@@ -293,9 +293,12 @@ fb_status lower(Plan &p) {
         s.scratch_bytes = conv_split_f32_scratch_bytes(p, s);
       }
       if (s.engine == ENGINE_TCGEN05) {
+        // (a smaller shape of a dynamic plan may fall to the CUDA-core kernel: keep its partials' room too)
+        const int64_t simt_bytes = d.op == FB_OP_CONV_WGRAD ? s.scratch_bytes : 0;
         s.split_k = 1;
         s.scratch_bytes = 0;
-        if (d.op == FB_OP_CONV_WGRAD) s.scratch_bytes = conv_wgrad_tc_scratch_bytes(p, s, &s.split_k);
+        if (d.op == FB_OP_CONV_WGRAD)
+          s.scratch_bytes = std::max(conv_wgrad_tc_scratch_bytes(p, s, &s.split_k), simt_bytes);
       }
       break;
     }

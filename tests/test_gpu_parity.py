@@ -80,6 +80,27 @@ def test_conv_wgrad_small_pixel_counts_on_tensor_cores(shape):
 
 
 @pytest.mark.parametrize("shape", [
+    (5, 64, 20, 12, 64, 3, 3, 1),     # ragged 8 x 8 patches, five images against stages of four
+    (3, 128, 16, 24, 128, 3, 3, 1),   # two 64-channel tiles, 128 output channels (two dY boxes per image)
+    (6, 64, 18, 18, 64, 3, 3, 0),     # no padding: 16 x 16 outputs
+    (5, 64, 16, 16, 128, 1, 3, 0),    # one filter row: a column's single tap
+    (9, 64, 16, 16, 64, 2, 2, 0),     # even filter: 15 x 15 outputs
+    (2, 64, 24, 24, 192, 3, 3, 1),    # two output-channel tiles
+])
+@pytest.mark.parametrize("dtype", [BF16, F16])
+def test_conv_wgrad_haloed_patches(shape, dtype):
+    """Weight gradients of narrow R x S > 1 layers: one CTA per filter column reads the column's taps as
+    shifted windows of one haloed X patch, several images per ring stage."""
+    n, c, h, w, k, r, s, pad = shape
+    per = {"dy": ("normal", 0.0, 0.01), "x": ("normal", 0.0, 0.05)}
+    g, ins, _ = wl.conv_wgrad(n, c, h, w, k, r, s, pad, dtype)
+    check_graph(g, _inputs(ins, 23, per=per))
+    assert "conv_wgrad_tcgen05" in g.statistics()
+    g, ins, _ = wl.conv_wgrad(n, c, h, w, k, r, s, pad, dtype, dw_dtype=F32)
+    check_graph(g, _inputs(ins, 24, per=per))
+
+
+@pytest.mark.parametrize("shape", [
     (2, 96, 30, 24, 160, 3, 3, 1),   # ragged channel block and ragged output-channel tile
     (1, 64, 32, 32, 64, 5, 5, 2),    # 5x5 taps, resident filter
     (1, 64, 34, 34, 128, 3, 3, 0),   # no padding: output 32x32

@@ -429,6 +429,14 @@ int wgrad_halo_max_c() {
   return c;
 }
 
+int wgrad_halo_min_taps() {
+  static const int c = [] {
+    const char *e = getenv("FUSILLI_B200_WGRAD_HALO_MINTAPS");
+    return e ? atoi(e) : 1;
+  }();
+  return c;
+}
+
 void wgrad_tiling(const WgradView &v, WgradTiling &t, bool allow_halo = true) {
   // 64-pixel patches with power-of-two sides (the K block must be exactly 64 rows)
   double best = -1.0;
@@ -457,7 +465,7 @@ void wgrad_tiling(const WgradView &v, WgradTiling &t, bool allow_halo = true) {
   // Haloed X patches (one CTA per filter column): 64-channel tiles, unit dilation, R taps = N <= 256, and
   // an image that 8 x 8 patches tile without much waste
   t.halo = 0;
-  if (allow_halo && taps > 1 && v.C <= wgrad_halo_max_c() && v.dil_h == 1 && v.dil_w == 1 && v.R <= 4 && v.S <= 8 && !wgrad_halo_off()) {
+  if (allow_halo && taps >= wgrad_halo_min_taps() && v.C <= wgrad_halo_max_c() && v.dil_h == 1 && v.dil_w == 1 && v.R <= 4 && v.S <= 8 && !wgrad_halo_off()) {
     const int64_t tiles = (int64_t)((v.Q + 7) / 8) * ((v.P + 7) / 8) * v.N;
     if ((double)v.N * v.P * v.Q / ((double)tiles * 64.0) >= 0.75) {
       t.halo = 1;

@@ -78,6 +78,7 @@ struct ConvTcParams {
   int32_t tma_store;                     // 16-bit output: stage tiles in shared memory, store them by TMA
   int32_t nacc, nacc_log2, acc_cols;     // TMEM accumulator ring: 2 or 4 tiles, acc_cols columns apart
   int32_t epi_alt;                       // epilogue groups of four warps take alternate tiles (BN = 64, staged stores)
+  int32_t pair_stages, pair_stage_bytes; // CTA-pair kernel: ring depth, bytes per stage (pixel box + half the filter rows)
   uint32_t *err;
   TcEpilogue epi;
 };
@@ -87,10 +88,16 @@ struct ConvTcParams {
 // quarter (warp index mod 4) and split the tile's columns in halves: on layers with few channel
 // blocks per tile the epilogue, not the MMAs, sets the pace. tfull0 / tempty0 are the barriers of
 // accumulator 0; accumulator 1's follow 8 bytes later.
+// `pair_rank` < 0: this CTA's tiles are blockIdx.x, + gridDim.x, ... and tempty0 is its own barrier. In the
+// CTA-pair kernel (`pair_rank` 0 or 1) cluster c takes the pairs c, c + clusters, ...; pair j is the pixel
+// tiles 2j and 2j+1 (the second may lie past the last image: nothing is loaded or stored for it) of one
+// channel tile, this CTA drains tile 2j + rank, and the accumulator is released on the LEADER's barrier.
 __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const CUtensorMap *tmap_c,
                                                     uint32_t staging, uint32_t tmem_base, uint32_t tfull0,
-                                                    uint32_t tempty0, int warp, int lane) {
+                                                    uint32_t tempty0, int warp, int lane, int pair_rank = -1) {
   const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
+  const bool paired = pair_rank >= 0;
+  const int pairs_pix = (tiles_pix + 1) / 2;
   const int q = warp & 3;
   const int set = (warp - 2) >> 2; // 0 or 1: which group of four warps this one belongs to
   // 64-channel tiles with staged stores: the two groups take alternate tiles, each warp all 64 columns
@@ -105,27 +112,37 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
   const int dw = row % p.bw, dh = (row / p.bw) % p.bh, dn = row / (p.bw * p.bh);
   const int64_t row_off0 = (int64_t)dn * p.out_sn + (int64_t)dh * p.out_sh + (int64_t)dw * p.out_sw;
   const uint32_t lt0 = alt ? (uint32_t)set : 0u, lt_step = alt ? 2u : 1u;
-  int64_t tile = (int64_t)blockIdx.x + (int64_t)lt0 * gridDim.x;
-  const int64_t tile_step = (int64_t)lt_step * gridDim.x;
-  int tw, th, tb, tno, sw, sh, sb, sno;
-  {
+  int64_t tile = paired ? (int64_t)(blockIdx.x >> 1) + (int64_t)lt0 * (gridDim.x >> 1) : (int64_t)blockIdx.x + (int64_t)lt0 * gridDim.x;
+  const int64_t tile_step = (int64_t)lt_step * (paired ? (gridDim.x >> 1) : gridDim.x);
+  const int64_t tile_end = paired ? (int64_t)pairs_pix * p.tiles_nout : (int64_t)p.total_tiles;
+  int tw = 0, th = 0, tb = 0, tno = 0, sw = 0, sh = 0, sb = 0, sno = 0;
+  if (!paired) {
     const int64_t tp = tile % tiles_pix, sp = tile_step % tiles_pix;
     tno = (int)(tile / tiles_pix); sno = (int)(tile_step / tiles_pix);
     tw = (int)(tp % p.tiles_w); th = (int)((tp / p.tiles_w) % p.tiles_h); tb = (int)(tp / (p.tiles_w * p.tiles_h));
     sw = (int)(sp % p.tiles_w); sh = (int)((sp / p.tiles_w) % p.tiles_h); sb = (int)(sp / (p.tiles_w * p.tiles_h));
   }
-  for (uint32_t lt = lt0; ok && tile < p.total_tiles; lt += lt_step, tile += tile_step) {
+  for (uint32_t lt = lt0; ok && tile < tile_end; lt += lt_step, tile += tile_step) {
     const int acc = (int)(lt & (uint32_t)(p.nacc - 1));
     const uint32_t aph = (lt >> p.nacc_log2) & 1;
+    if (paired) {
+      // long reductions per tile: the divisions are not what bounds these layers
+      const int tp = 2 * (int)(tile % pairs_pix) + pair_rank;
+      tno = (int)(tile / pairs_pix);
+      tw = tp % p.tiles_w; th = (tp / p.tiles_w) % p.tiles_h; tb = tp / (p.tiles_w * p.tiles_h); // tb == tiles_nb: past the end
+    }
     const int w = tw * p.bw + dw, h = th * p.bh + dh, n = tb * p.bn + dn;
     const bool row_ok = row < p.rows && w < p.W && h < p.H && n < p.N;
     const int64_t row_off = row_off0 + (int64_t)(tb * p.bn) * p.out_sn + (int64_t)(th * p.bh) * p.out_sh +
                             (int64_t)(tw * p.bw) * p.out_sw;
     const int tw_c = tw, th_c = th, tb_c = tb, tno_c = tno; // this tile's digits; advance for the next one
-    tw += sw; if (tw >= p.tiles_w) { tw -= p.tiles_w; ++th; }
-    th += sh; if (th >= p.tiles_h) { th -= p.tiles_h; ++tb; }
-    tb += sb; if (tb >= p.tiles_nb) { tb -= p.tiles_nb; ++tno; }
-    tno += sno;
+    const bool tile_ok = tb_c < p.tiles_nb;
+    if (!paired) {
+      tw += sw; if (tw >= p.tiles_w) { tw -= p.tiles_w; ++th; }
+      th += sh; if (th >= p.tiles_h) { th -= p.tiles_h; ++tb; }
+      tb += sb; if (tb >= p.tiles_nb) { tb -= p.tiles_nb; ++tno; }
+      tno += sno;
+    }
     TR_BEGIN;
     if (!mbar_wait(tfull0 + 8u * acc, aph, p.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
     if (warp == 2) TR_ADD(5); // epilogue: waiting for a finished accumulator
@@ -181,7 +198,10 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
       auto release_accumulator = [&]() {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+        if (lane == 0) {
+          if (paired) mbar_arrive_cluster(map_to_cta(tempty0 + 8u * acc, 0));
+          else mbar_arrive(tempty0 + 8u * acc);
+        }
       };
       uint32_t raw_a[32], raw_b[32];
       tmem_ld_32x32(taddr + c_begin * 32, raw_a);
@@ -196,7 +216,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
         if (warp == 2) TR_ADD(8);
         named_barrier_sync(bar_id, bar_threads);
         if (warp == 2) TR_ADD(9);
-        if (issuer) {
+        if (issuer && tile_ok) {
           tma_store_4d(tmap_c, buf, no0, tw_c * p.bw, th_c * p.bh, tb_c * p.bn);
           tma_store_commit();
         }
@@ -220,7 +240,7 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
         fence_proxy_async();
         named_barrier_sync(bar_id, bar_threads);
         if (warp == 2) TR_ADD(9); // epilogue: barrier
-        if (issuer) {
+        if (issuer && tile_ok) {
           tma_store_4d(tmap_c, buf, no0 + box_col0, tw_c * p.bw, th_c * p.bh, tb_c * p.bn);
           tma_store_commit();
         }
@@ -235,7 +255,10 @@ __device__ __forceinline__ void conv_epilogue_warps(const ConvTcParams &p, const
       if (c == c_end - 1) {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty0 + 8u * acc);
+        if (lane == 0) {
+          if (paired) mbar_arrive_cluster(map_to_cta(tempty0 + 8u * acc, 0));
+          else mbar_arrive(tempty0 + 8u * acc);
+        }
       }
       const int nc = no0 + c * 32;
       if (row_ok && nc < p.Nout) {
@@ -378,6 +401,164 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   }
 }
 
+
+// CTA-pair variant of the per-tap kernel for tiles of 128 or 256 output channels (cta_group::2): the two
+// CTAs of a cluster work on two neighbouring 128-pixel tiles of one channel tile. Each loads its own
+// pixel boxes and only ITS HALF of the filter rows of a K block; one MMA of 256 x BN x 16, issued by the
+// even CTA, reads both halves and writes each CTA's 128 accumulator rows into that CTA's TMEM. Per CTA and
+// K block that is 16 KB + BN/2 x 128 bytes instead of 16 KB + BN x 128 for the same math: six or eight ring
+// stages instead of four or six, and one issuing warp (whose barrier waits cost 230-320 clk each even when
+// the barrier is complete) for two tiles. No load is multicast: every CTA fetches its own operands; only
+// barrier arrivals cross between the two CTAs.
+constexpr int PAIR_MAX_STAGES = 8;
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS_TAP, 1)
+conv_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // the same offset in both CTAs
+  const int STAGES = p.pair_stages;
+  const uint32_t STAGE_BYTES = (uint32_t)p.pair_stage_bytes;
+  const uint32_t bar_base = smem_base + RING_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                       // used in the leader only
+  auto empty_bar = [&](int s) { return bar_base + 8u * (PAIR_MAX_STAGES + s); };  // each CTA's own
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * PAIR_MAX_STAGES + a); };      // each CTA's own
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * PAIR_MAX_STAGES + 2 + a); }; // the leader's
+  const uint32_t tmem_slot = bar_base + 8u * (2 * PAIR_MAX_STAGES + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank(); // 0 = leader
+  const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);  // one expect_tx arrival, the bytes of both CTAs
+      mbar_init(empty_bar(s), 1); // committed to by the leader's MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 16); // eight epilogue warps of each CTA
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    if (p.tma_store) tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS); // one warp of each CTA of the pair, collectively
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  uint32_t tmem_base;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int kblocks = p.R * p.S * p.cblocks;
+  const int tiles_pix = p.tiles_w * p.tiles_h * p.tiles_nb;
+  const int pairs_pix = (tiles_pix + 1) / 2;
+  const int total_pairs = pairs_pix * p.tiles_nout;
+  const int half_n = p.BN / 2;
+  const uint32_t stage_tx = 2u * (p.a_bytes + (uint32_t)half_n * BK * 2);
+
+  if (warp == 0 || warp == NUM_THREADS / 32) {
+    // two producer warps on alternate K blocks, as in the single-CTA kernel: whole warp in the loop,
+    // elected lane issues
+    const uint32_t pid = warp == 0 ? 0u : 1u;
+    uint32_t it = 0;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int w = cluster_id; w < total_pairs && ok; w += nclusters) {
+      const int tp = 2 * (w % pairs_pix) + (int)rank, tno = w / pairs_pix;
+      // a pixel tile past the last image (odd tile count) has tb == tiles_nb: its boxes lie outside
+      // the tensor and arrive as zeros
+      const int tw = tp % p.tiles_w, th = (tp / p.tiles_w) % p.tiles_h, tb = tp / (p.tiles_w * p.tiles_h);
+      const int w0 = tw * p.bw + p.off_w, h0 = th * p.bh + p.off_h, n0 = tb * p.bn;
+      const int no0 = tno * p.BN + (int)rank * half_n; // this CTA's half of the channel tile
+      int cb = 0, ts = 0, tr = 0;
+      for (int kb = 0; kb < kblocks; ++kb, ++it, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+        if ((it & 1u) == pid) {
+          TR_BEGIN;
+          if (!mbar_wait_warp(empty_bar(s), ph ^ 1, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          if (warp == 0) TR_ADD(10);
+          const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+          if (rank == 0) mbar_expect_tx_elect(full_bar(s), stage_tx);
+          const uint32_t sa = smem_base + (uint32_t)s * STAGE_BYTES, sb = sa + A_BYTES;
+          const int c0 = cb * BK;
+          tma_load_4d_pair_elect(sa, &tmap_a, lead_full, c0, w0 + ts * p.step_w, h0 + tr * p.step_h, n0);
+          if (!p.dgrad) {
+            tma_load_4d_pair_elect(sb, &tmap_b, lead_full, c0, ts, tr, no0); // box of BN/2 filter rows
+          } else {
+            for (int i = 0; i < half_n / 64; ++i)
+              tma_load_4d_pair_elect(sb + i * (64 * BK * 2), &tmap_b, lead_full, no0 + 64 * i, ts, tr, c0);
+          }
+          if (warp == 0) TR_ADD(11);
+        }
+        if (++cb == p.cblocks) {
+          cb = 0;
+          if (++ts == p.S) {
+            ts = 0;
+            ++tr;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 0) {
+      const uint32_t idesc = make_idesc_f16(2 * BM, p.BN, p.ab_format, 0, p.dgrad);
+      const uint32_t b_lbo = p.dgrad ? 64 * BK * 2 : 16, b_kstep = p.dgrad ? 2048 : 32;
+      const uint64_t a_desc0 = make_smem_desc(smem_base, 16, 1024);
+      const uint64_t b_desc0 = make_smem_desc(smem_base + A_BYTES, b_lbo, 1024);
+      uint32_t lt = 0, ph = 0;
+      int s = 0;
+      bool ok = true;
+      // The NEXT stage's barrier is tested before a stage's MMAs are issued and the answer looked at after
+      // them: a wait costs the warp 230-320 clk even on a completed barrier.
+      uint32_t peek = mbar_peek_elect(full_bar(0), 0);
+      for (int w = cluster_id; w < total_pairs && ok; w += nclusters, ++lt) {
+        const int acc = lt & 1;
+        const uint32_t aph = (lt >> 1) & 1;
+        TR_BEGIN;
+        if (!mbar_wait_warp(tempty_bar(acc), aph ^ 1, p.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        TR_ADD(12);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * MAX_BN;
+        for (int kb = 0; kb < kblocks; ++kb, s = (s + 1 == STAGES) ? 0 : s + 1, ph ^= (s == 0)) {
+          if (!__any_sync(0xffffffffu, peek != 0) && !mbar_wait_warp(full_bar(s), ph, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          TR_ADD(13);
+          tc_fence_after();
+          {
+            const int sn = (s + 1 == STAGES) ? 0 : s + 1;
+            peek = mbar_peek_elect(full_bar(sn), ph ^ (uint32_t)(sn == 0));
+          }
+          const uint64_t soff = (uint64_t)(((uint32_t)s * STAGE_BYTES) >> 4);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)
+            tc_mma_f16_pair_elect(d_tmem, a_desc0 + soff + (uint64_t)((k * 32) >> 4),
+                                  b_desc0 + soff + (uint64_t)((k * b_kstep) >> 4), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          tc_commit_pair_elect(map_to_cta(empty_bar(s), 0));
+          tc_commit_pair_elect(map_to_cta(empty_bar(s), 1));
+          TR_ADD(14);
+        }
+        if (ok) { // accumulator complete, in both CTAs' TMEM
+          tc_commit_pair_elect(map_to_cta(tfull_bar(acc), 0));
+          tc_commit_pair_elect(map_to_cta(tfull_bar(acc), 1));
+        }
+      }
+    }
+  } else {
+    conv_epilogue_warps(p, &tmap_c, smem_base + RING_BYTES_STAGED, tmem_base, tfull_bar(0), tempty_bar(0), warp, lane,
+                        (int)rank);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // neither CTA leaves while the other may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
 
 // Halo variant for R x S > 1 (unit stride and dilation): the tile is 8 x 16 output pixels of one
 // image. Per 64-channel block the producer loads S column-shifted patches of 8 x (16+R-1) input
@@ -607,6 +788,44 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   }
 }
 
+// Whether clusters of two CTAs of the pair kernel can be resident on this device (asked once per device),
+// and whether the caller left the pair kernel enabled.
+static bool conv_pair_usable(int device) {
+  static const bool enabled = [] {
+    const char *e = getenv("FUSILLI_B200_CONV_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled || device < 0 || device >= 64) return false;
+  static std::mutex mu;
+  static int8_t state[64] = {0}; // 0 unknown, 1 usable, -1 not
+  std::lock_guard<std::mutex> lock(mu);
+  if (state[device] == 0) {
+    state[device] = -1;
+    if (set_max_dynamic_smem(reinterpret_cast<const void *>(conv_pair_tcgen05_kernel), SMEM_BYTES, device) ==
+        cudaSuccess) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS_TAP, 1, 1);
+      cfg.dynamicSmemBytes = SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void *>(conv_pair_tcgen05_kernel), &cfg) ==
+              cudaSuccess &&
+          n >= 1)
+        state[device] = 1;
+    }
+    (void)cudaGetLastError();
+  }
+  return state[device] == 1;
+}
+
 // ---- host -----------------------------------------------------------------------------
 
 struct ConvView {
@@ -819,6 +1038,17 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
       p.b_stages = (int)std::min<int64_t>(HALO_MAX_B_STAGES, (ring_bytes - 2 * p.a_slot_bytes) / p.b_bytes);
     }
   }
+  // CTA pairs on tiles of 128 / 256 channels with at least eight K blocks per tile: a stage is 24 / 32 KB per
+  // CTA instead of 32 / 48 KB (more stages round the ring, whose round trip sets the pace of the single-CTA
+  // kernel on these layers) and one issuing warp serves two tiles. Measured: 28x28 C128 3x3 68.6 -> 64.5 us
+  // fprop, 72.7 -> 66.6 dgrad; 7x7 C512 3x3 62.4 -> 58.4 / 60.4; 14x14 1024 -> 256 dgrad 35.8 -> 33.8; with only
+  // four K blocks (14x14 256 -> 1024 fprop) the pair is slower (56 against 46 us) and is not taken.
+  // FUSILLI_B200_CONV_PAIR=0 keeps the single-CTA kernel.
+  const int tiles_pix_all = p.tiles_w * p.tiles_h * p.tiles_nb;
+  const bool use_pair = !halo && p.BN >= 128 && p.R * p.S * p.cblocks >= 8 && tiles_pix_all >= 2 &&
+                        conv_pair_usable(cx.dev->ordinal);
+  p.pair_stage_bytes = A_BYTES + (p.BN / 2) * BK * 2;
+  p.pair_stages = std::min(PAIR_MAX_STAGES, ring_bytes / p.pair_stage_bytes);
   p.out = optr;
   p.err = cx.dev->error_word;
   p.epi.num_ops = s.num_epilogue;
@@ -851,7 +1081,7 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     const int64_t Cf = wt.dims[1];
     uint64_t w_dims[4] = {(uint64_t)Cf, (uint64_t)v.S, (uint64_t)v.R, (uint64_t)wt.dims[0]};
     uint64_t w_str[3] = {(uint64_t)Cf * 2, (uint64_t)v.S * Cf * 2, (uint64_t)v.R * v.S * Cf * 2};
-    uint32_t wbox_f[4] = {BK, 1, 1, (uint32_t)p.BN};
+    uint32_t wbox_f[4] = {BK, 1, 1, (uint32_t)(use_pair ? p.BN / 2 : p.BN)}; // a CTA of a pair loads half the rows
     uint32_t wbox_d[4] = {64, 1, 1, BK};
     FB_REQUIRE(encode_tmap_2byte(&tmB, wptr, 4, w_dims, w_str, v.dgrad ? wbox_d : wbox_f, &why),
                FB_RUNTIME_FAILURE, why);
@@ -874,6 +1104,15 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     } else {
       tmC = tmA; // unused by the kernel
     }
+  }
+  if (use_pair) {
+    cudaError_t pe = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_pair_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
+    FB_REQUIRE(pe == cudaSuccess, FB_RUNTIME_FAILURE,
+               std::string("conv_pair_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(pe));
+    const int total_pairs = ((tiles_pix_all + 1) / 2) * p.tiles_nout;
+    const int clusters = std::min<int>(total_pairs, cx.dev->sm_count / 2);
+    conv_pair_tcgen05_kernel<<<2 * clusters, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
+    return FB_OK;
   }
   cudaError_t ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,

@@ -79,6 +79,21 @@ def test_conv_wgrad_small_pixel_counts_on_tensor_cores(shape):
     check_graph(g, _inputs(ins, 18, per={"dy": ("normal", 0.0, 0.01), "x": ("normal", 0.0, 0.05)}))
 
 
+@pytest.mark.parametrize("n", [5, 6, 7])
+@pytest.mark.parametrize("k", [128, 256, 192])
+def test_conv_wide_layers_on_cta_pairs(n, k):
+    """128- and 256-channel tiles with at least eight K blocks run on clusters of two CTAs (two neighbouring
+    pixel tiles per 256-row MMA); batch sizes that give even and odd tile counts (an odd count leaves the last
+    pair's second tile past the end of the tensor), a ragged channel tile (192), fused bias + ReLU, dgrad."""
+    c, h, w, r, s, pad = 128, 14, 14, 3, 3, 1
+    x_dist, dy_dist = ("normal", 0.0, 0.05), ("normal", 0.0, 0.01)
+    g, ins, _ = wl.conv_fprop_bias_relu(n, c, h, w, k, r, s, pad, BF16)
+    check_graph(g, _inputs(ins, 31, x_dist, per={"bias": ("uniform", -0.1, 0.1)}))
+    assert "conv_fprop_tcgen05" in g.statistics()
+    g, ins, _ = wl.conv_dgrad(n, c, h, w, k, r, s, pad, BF16)
+    check_graph(g, _inputs(ins, 32, per={"dy": dy_dist, "w": x_dist}))
+
+
 @pytest.mark.parametrize("shape", [
     (5, 64, 20, 12, 64, 3, 3, 1),     # ragged 8 x 8 patches, five images against stages of four
     (3, 128, 16, 24, 128, 3, 3, 1),   # two 64-channel tiles, 128 output channels (two dY boxes per image)

@@ -69,6 +69,8 @@ struct SplitParams {
 __global__ void __launch_bounds__(256)
 split3_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ xs, int64_t x_rows,
                    const float *__restrict__ w, __nv_bfloat16 *__restrict__ ws, int64_t w_rows, int C) {
+  pdl_launch_dependents();
+  pdl_wait(); // (the scratch this kernel overwrites may still be read by the launch before it)
   const int64_t vec_per_row = C / 4;
   const int64_t x_total = x_rows * vec_per_row, total = x_total + w_rows * vec_per_row;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -100,6 +102,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_split_f32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                               const SplitParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int STAGES = p.stages;
   const uint32_t STAGE_BYTES = (uint32_t)p.stage_bytes;
@@ -131,6 +134,7 @@ conv_split_f32_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -485,7 +489,7 @@ fb_status launch_conv_split_f32(const ExecContext &cx, const Step &s) {
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("conv_split_f32: cannot reserve shared memory: ") + cudaGetErrorString(ae));
   const int grid = std::min<int>(p.total_tiles, cx.dev->sm_count);
-  conv_split_f32_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+  FB_CUDA_OK(launch_pdl(conv_split_f32_tcgen05_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, cx.dev->stream, tmA, tmB, p));
   return FB_OK;
 }
 

@@ -280,6 +280,7 @@ __global__ void __launch_bounds__(NUM_THREADS_TAP, 1)
 conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int STAGES = p.stages;
   const uint32_t STAGE_BYTES = (uint32_t)p.stage_bytes;
@@ -312,6 +313,7 @@ conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -415,6 +417,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS_TAP, 1)
 conv_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // the same offset in both CTAs
   const int STAGES = p.pair_stages;
   const uint32_t STAGE_BYTES = (uint32_t)p.pair_stage_bytes;
@@ -450,6 +453,7 @@ conv_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   __syncthreads();
   cluster_sync_all(); // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -578,6 +582,7 @@ __global__ void __launch_bounds__(NUM_THREADS_HALO, 1)
 conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ CUtensorMap tmap_c, const ConvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sb_base = smem_base + (uint32_t)(p.a_slots * p.a_slot_bytes);
   const uint32_t bar_base = smem_base + RING_BYTES;
@@ -616,6 +621,7 @@ conv_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -1111,7 +1117,8 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
                std::string("conv_pair_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(pe));
     const int total_pairs = ((tiles_pix_all + 1) / 2) * p.tiles_nout;
     const int clusters = std::min<int>(total_pairs, cx.dev->sm_count / 2);
-    conv_pair_tcgen05_kernel<<<2 * clusters, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
+    FB_CUDA_OK(launch_pdl(conv_pair_tcgen05_kernel, dim3(2 * clusters), dim3(NUM_THREADS_TAP), SMEM_BYTES, cx.dev->stream, tmA, tmB,
+                          tmC, p));
     return FB_OK;
   }
   cudaError_t ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
@@ -1122,10 +1129,10 @@ fb_status launch_conv_tc(const ExecContext &cx, const Step &s) {
     ae = set_max_dynamic_smem(reinterpret_cast<const void *>(conv_halo_tcgen05_kernel), SMEM_BYTES, cx.dev->ordinal);
     FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
                std::string("conv_halo_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
-    conv_halo_tcgen05_kernel<<<grid, NUM_THREADS_HALO, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
+    FB_CUDA_OK(launch_pdl(conv_halo_tcgen05_kernel, dim3(grid), dim3(NUM_THREADS_HALO), SMEM_BYTES, cx.dev->stream, tmA, tmB, tmC, p));
     return FB_OK;
   }
-  conv_tcgen05_kernel<<<grid, NUM_THREADS_TAP, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, tmC, p);
+  FB_CUDA_OK(launch_pdl(conv_tcgen05_kernel, dim3(grid), dim3(NUM_THREADS_TAP), SMEM_BYTES, cx.dev->stream, tmA, tmB, tmC, p));
   return FB_OK;
 }
 

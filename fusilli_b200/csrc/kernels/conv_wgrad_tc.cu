@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
                           const WgradTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int A_STAGES = p.a_stages, B_STAGES = p.b_stages;
   const uint32_t A_STAGE_BYTES = (uint32_t)p.a_stage_bytes, B_STAGE_BYTES = (uint32_t)p.b_stage_bytes;
@@ -106,6 +107,7 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -332,6 +334,8 @@ conv_wgrad_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __g
 // latency-bound) and their sums are combined pairwise, (g0 + g1) + (g2 + g3).
 __global__ void __launch_bounds__(256)
 wgrad_slice_reduce_kernel(const float *__restrict__ partial, void *out, int out_dtype, int64_t elems, int slices) {
+  pdl_launch_dependents();
+  pdl_wait(); // the partials are complete and visible after this
   const int g = threadIdx.x & 3;
   const int64_t per_block = blockDim.x / 4;
   for (int64_t i0 = (int64_t)blockIdx.x * per_block; i0 < elems; i0 += (int64_t)gridDim.x * per_block) {
@@ -358,6 +362,8 @@ wgrad_slice_reduce_kernel(const float *__restrict__ partial, void *out, int out_
 // spread).
 __global__ void __launch_bounds__(256)
 wgrad_slice_reduce1_kernel(const float *__restrict__ partial, void *out, int out_dtype, int64_t elems, int slices) {
+  pdl_launch_dependents();
+  pdl_wait(); // the partials are complete and visible after this
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += (int64_t)gridDim.x * blockDim.x) {
     float acc = 0.f;
     int s = 0;
@@ -583,13 +589,15 @@ fb_status launch_conv_wgrad_tc(const ExecContext &cx, const Step &s) {
   FB_REQUIRE(ae == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("conv_wgrad_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(ae));
   const int grid = t.k_tiles * t.c_tiles * t.ngroups * t.slices;
-  conv_wgrad_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmDy, tmX, p);
+  FB_CUDA_OK(launch_pdl(conv_wgrad_tcgen05_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, cx.dev->stream, tmDy, tmX, p));
   if (t.slices >= 16) {
     const int rblocks = (int)std::min<int64_t>((elems + 63) / 64, (int64_t)cx.dev->sm_count * 8);
-    wgrad_slice_reduce_kernel<<<rblocks, 256, 0, cx.dev->stream>>>(p.partial, dwp, dw.dtype, elems, t.slices);
+    FB_CUDA_OK(launch_pdl(wgrad_slice_reduce_kernel, dim3(rblocks), dim3(256), 0, cx.dev->stream, (const float *)p.partial, dwp,
+                          (int)dw.dtype, elems, (int)t.slices));
   } else {
     const int rblocks = (int)std::min<int64_t>((elems + 255) / 256, (int64_t)cx.dev->sm_count * 8);
-    wgrad_slice_reduce1_kernel<<<rblocks, 256, 0, cx.dev->stream>>>(p.partial, dwp, dw.dtype, elems, t.slices);
+    FB_CUDA_OK(launch_pdl(wgrad_slice_reduce1_kernel, dim3(rblocks), dim3(256), 0, cx.dev->stream, (const float *)p.partial, dwp,
+                          (int)dw.dtype, elems, (int)t.slices));
   }
   return FB_OK;
 }

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -108,6 +109,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -275,6 +277,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                          const GemmTcParams p) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u; // the same offset in both CTAs
   const uint32_t bar_base = smem_base + pair::STAGES * pair::STAGE_BYTES;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -307,6 +310,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   __syncthreads();
   cluster_sync_all(); // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -544,6 +548,14 @@ bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint6
 }
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize is per function and device: set once, not per launch.
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("FUSILLI_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 cudaError_t set_max_dynamic_smem(const void *func, int bytes, int device) {
   if (!launch_cache_enabled()) return cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
   static std::mutex mu;
@@ -808,7 +820,8 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
     FB_REQUIRE(pe == cudaSuccess, FB_RUNTIME_FAILURE,
                std::string("gemm_pair_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(pe));
     const int clusters = std::min<int>(p.total_work, cx.dev->sm_count / 2);
-    gemm_pair_tcgen05_kernel<<<2 * clusters, NUM_THREADS, pair::SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+    FB_CUDA_OK(launch_pdl(gemm_pair_tcgen05_kernel, dim3(2 * clusters), dim3(NUM_THREADS), pair::SMEM_BYTES, cx.dev->stream, tmA,
+                          tmB, p));
     return FB_OK;
   }
   cudaError_t attr_err =
@@ -816,7 +829,7 @@ fb_status launch_gemm_tc(const ExecContext &cx, const Step &s) {
   FB_REQUIRE(attr_err == cudaSuccess, FB_RUNTIME_FAILURE,
              std::string("gemm_tcgen05: cannot reserve shared memory: ") + cudaGetErrorString(attr_err));
   int grid = std::min<int>(p.total_work, cx.dev->sm_count);
-  gemm_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tmA, tmB, p);
+  FB_CUDA_OK(launch_pdl(gemm_tcgen05_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, cx.dev->stream, tmA, tmB, p));
   return FB_OK;
 }
 

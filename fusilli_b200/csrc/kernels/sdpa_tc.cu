@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const SdpaTcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents(); // the next kernel's CTAs may take the SMs this kernel's CTAs leave
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + SM_BARS;
   // barrier slots
@@ -198,6 +199,7 @@ sdpa_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait(); // nothing before this line touches global memory; the kernels before this one are complete after it
   uint32_t tmem_base;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
@@ -540,7 +542,7 @@ fb_status launch_sdpa_tc(const ExecContext &cx, const Step &s) {
   FB_REQUIRE(pairs < (1ll << 31), FB_NOT_IMPLEMENTED, "sdpa_tcgen05: too many query blocks");
   p.total_pairs = (int)pairs;
   const int grid = (int)std::min<int64_t>(pairs, cx.dev->sm_count);
-  sdpa_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, cx.dev->stream>>>(tq, tk, tv, p);
+  FB_CUDA_OK(launch_pdl(sdpa_tcgen05_kernel, dim3(grid), dim3(NUM_THREADS), SMEM_BYTES, cx.dev->stream, tq, tk, tv, p));
   return FB_OK;
 }
 

@@ -8,6 +8,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 namespace fb {
 namespace sm100 {
@@ -276,6 +277,16 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// ---- programmatic dependent launch --------------------------------------------------------
+// A kernel launched with launch_pdl() may start while the kernel before it in the stream is still running
+// (its CTAs take the SMs the earlier kernel's CTAs leave). pdl_launch_dependents() at the top lets the NEXT
+// kernel do the same; pdl_wait(), which every thread executes after the kernel's set-up (barriers, TMEM,
+// descriptor prefetch) and before anything touches global memory, returns once the earlier kernels have
+// completed and their writes are visible. Launch latency and set-up then overlap the tail of the kernel
+// before. Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- CTA pairs (cta_group::2) ---------------------------------------------------------
 // Two CTAs of a cluster of two run ONE MMA over a 256-row tile: each holds its own 128 rows of A
 // and its own half of B in shared memory at the SAME offsets, and its 128 rows of the accumulator
@@ -394,6 +405,29 @@ bool encode_tmap_2byte(CUtensorMap *map, const void *base, int rank, const uint6
                        const uint64_t *strides_bytes, const uint32_t *box, const char **why);
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of per launch.
 cudaError_t set_max_dynamic_smem(const void *func, int bytes, int device);
+// Whether kernels are launched with programmatic stream serialization (FUSILLI_B200_PDL=0 turns it off).
+bool pdl_enabled();
+
+#if defined(__CUDACC__)
+// Launch of a kernel that calls pdl_wait() before its first global access (see above).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 } // namespace sm100
 } // namespace fb
